@@ -151,10 +151,21 @@ __device__ __forceinline__ void qk_product(float (&s)[NT][4], const bf16* q_rows
 // Online-softmax update with the scores of NT*8 keys, then O += P . V.
 // key_pos0: position of key column 0; row_pos[2]: positions of this thread's rows
 // (negative = row unused); keys outside [row_lo, row_pos] are masked.
+// chunk > 0: a query sees only the keys of its own chunk of positions, [floor(pos / chunk) chunk, pos];
+// cap_log2 > 0: scores are capped, s -> cap tanh(s scale / cap), with cap_log2 = cap log2(e), inv_cap = scale / cap.
+struct Cap {
+  int chunk;
+  float cap_log2;
+  float inv_cap;
+};
+__device__ __forceinline__ int chunk_lo(int lo, int pos, int chunk) {
+  return (chunk > 0 && pos >= 0) ? max(lo, (pos / chunk) * chunk) : lo;
+}
+
 template <int NT>
 __device__ __forceinline__ void softmax_pv(RowState& st, float (&s)[NT][4], const bf16* v_tile, int key_pos0,
                                            const int (&row_pos)[2], const int (&row_lo)[2], float scale_log2,
-                                           int lane) {
+                                           const Cap& cap, int lane) {
   const int c = lane & 3;
   float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
@@ -164,7 +175,9 @@ __device__ __forceinline__ void softmax_pv(RowState& st, float (&s)[NT][4], cons
       const int r = e >> 1;
       const int kp = key_pos0 + j * 8 + 2 * c + (e & 1);
       const bool ok = kp <= row_pos[r] && kp >= row_lo[r];
-      s[j][e] = ok ? s[j][e] * scale_log2 : -CUDART_INF_F;
+      // with a cap c the score s becomes c tanh(s / c), here in units of log2(e)
+      const float sc = cap.cap_log2 > 0.0f ? cap.cap_log2 * tanhf(s[j][e] * cap.inv_cap) : s[j][e] * scale_log2;
+      s[j][e] = ok ? sc : -CUDART_INF_F;
       mx[r] = fmaxf(mx[r], s[j][e]);
     }
   }
@@ -216,7 +229,7 @@ __device__ __forceinline__ void softmax_pv(RowState& st, float (&s)[NT][4], cons
 __global__ void __launch_bounds__(THREADS) prefill_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     bf16* __restrict__ out, const int* __restrict__ block_table, const int* __restrict__ q_start,
-    const int* __restrict__ kv_len, int nh, int nkv, int max_pages, int window, float scale_log2) {
+    const int* __restrict__ kv_len, int nh, int nkv, int max_pages, int window, float scale_log2, Cap cap) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   jb::pdl_launch_dependents();
   jb::pdl_wait();
@@ -247,7 +260,7 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
   }
   const int pos_last = pos0 + n_tok - 1;
   const int kb_end = pos_last / PAGE;
-  const int kb_start = window > 0 ? max(0, pos0 - window + 1) / PAGE : 0;
+  const int kb_start = chunk_lo(window > 0 ? max(0, pos0 - window + 1) : 0, pos0, cap.chunk) / PAGE;
   auto issue = [&](int kb, int stage) {
     const size_t page = (size_t)pages[kb];
     const size_t off = (page * nkv + kvh) * PAGE * HD;
@@ -263,7 +276,7 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
     const int row = warp * 16 + (lane >> 2) + 8 * r;
     const int tl = row / G;
     row_pos[r] = tl < n_tok ? pos0 + tl : -1;
-    row_lo[r] = window > 0 ? max(0, row_pos[r] - window + 1) : 0;
+    row_lo[r] = chunk_lo(window > 0 ? max(0, row_pos[r] - window + 1) : 0, row_pos[r], cap.chunk);
   }
   RowState st;
   st.init();
@@ -280,7 +293,7 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
     const bf16* k_tile = kv_s + (size_t)stage * 2 * KV_TILE;
     float s[8][4];
     qk_product<8>(s, q_s + warp * 16 * LD, k_tile, lane);
-    softmax_pv<8>(st, s, k_tile + KV_TILE, kb * PAGE, row_pos, row_lo, scale_log2, lane);
+    softmax_pv<8>(st, s, k_tile + KV_TILE, kb * PAGE, row_pos, row_lo, scale_log2, cap, lane);
     __syncthreads();
   }
 #pragma unroll
@@ -333,7 +346,7 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ block_table, const int* __restrict__ kv_len, int nh, int nkv, int max_pages,
-    int window, float scale_log2, int n_splits, FusedInput fused) {
+    int window, float scale_log2, int n_splits, FusedInput fused, Cap cap) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   jb::pdl_launch_dependents();
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [16][LD]
@@ -345,7 +358,7 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
   const int g0 = rb * 16, n_rows = min(16, G - g0);
   const int len = kv_len[seq];
   const int pos = len - 1;                        // the one new token is the sequence's last
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = chunk_lo(window > 0 ? max(0, pos - window + 1) : 0, pos, cap.chunk);
   const int kb_first = lo / PAGE, kb_last = pos / PAGE;
   const int n_blocks = kb_last - kb_first + 1;
   // the pages are cut evenly: split s walks pages [s n / S, (s + 1) n / S), so that no split is left
@@ -464,7 +477,7 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
       float s[2][4];
       qk_product<2>(s, q_s, k_tile + warp * 16 * LD, lane);
       softmax_pv<2>(st, s, k_tile + KV_TILE + warp * 16 * LD, kb * PAGE + warp * 16, row_pos, row_lo,
-                    scale_log2, lane);
+                    scale_log2, cap, lane);
       __syncwarp();  // the warp is done with its rows of this stage before its next loads overwrite them
     }
   }
@@ -567,7 +580,8 @@ int decode_stages_for(long long ctas, int pages_per_cta) {
 template <int ST>
 cudaError_t decode_go(dim3 grid, cudaStream_t stream, bool pdl, const bf16* q, const bf16* k_cache, const bf16* v_cache,
                       bf16* out, float* part_o, float* part_ml, const int* block_table, const int* kv_len, int nh,
-                      int nkv, int max_pages, int window, float scale_log2, int n_splits, const FusedInput& fused) {
+                      int nkv, int max_pages, int window, float scale_log2, int n_splits, const FusedInput& fused,
+                      const Cap& cap) {
   static bool configured = false;   // one flag per ring depth
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(decode_kernel<ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem(ST));
@@ -577,11 +591,11 @@ cudaError_t decode_go(dim3 grid, cudaStream_t stream, bool pdl, const bf16* q, c
   if (pdl) {
     jb::Launch cfg(grid, dim3(THREADS), decode_smem(ST), stream);
     return cudaLaunchKernelEx(&cfg.c, decode_kernel<ST>, q, k_cache, v_cache, out, part_o, part_ml, block_table, kv_len,
-                              nh, nkv, max_pages, window, scale_log2, n_splits, fused);
+                              nh, nkv, max_pages, window, scale_log2, n_splits, fused, cap);
   }
   decode_kernel<ST><<<grid, THREADS, decode_smem(ST), stream>>>(q, k_cache, v_cache, out, part_o, part_ml, block_table,
                                                                kv_len, nh, nkv, max_pages, window, scale_log2, n_splits,
-                                                               fused);
+                                                               fused, cap);
   return cudaGetLastError();
 }
 
@@ -589,12 +603,12 @@ cudaError_t decode_go(dim3 grid, cudaStream_t stream, bool pdl, const bf16* q, c
 cudaError_t decode_dispatch(dim3 grid, cudaStream_t stream, bool pdl, const bf16* q, const bf16* k_cache,
                             const bf16* v_cache, bf16* out, float* part_o, float* part_ml, const int* block_table,
                             const int* kv_len, int nh, int nkv, int max_pages, int window, float scale_log2,
-                            int n_splits, const FusedInput& fused) {
+                            int n_splits, const FusedInput& fused, const Cap& cap = Cap{0, 0.0f, 0.0f}) {
   const long long ctas = (long long)grid.x * grid.y * grid.z;
   const int stages = decode_stages_for(ctas, max(1, max_pages / max(1, n_splits)));
 #define JB_DECODE_GO(ST)                                                                                      \
   return decode_go<ST>(grid, stream, pdl, q, k_cache, v_cache, out, part_o, part_ml, block_table, kv_len, nh, nkv, \
-                       max_pages, window, scale_log2, n_splits, fused)
+                       max_pages, window, scale_log2, n_splits, fused, cap)
   switch (stages) {
     case 2: JB_DECODE_GO(2);
     case 5: JB_DECODE_GO(5);
@@ -610,10 +624,15 @@ cudaError_t decode_dispatch(dim3 grid, cudaStream_t stream, bool pdl, const bf16
 
 JB_EXPORT int jb_attention_bf16_head_dim() { return HD; }
 
-JB_EXPORT int jb_attention_bf16_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
+namespace {
+Cap make_cap(int chunk, float softcap, float scale) {
+  return softcap > 0.0f ? Cap{chunk, softcap * LOG2E, scale / softcap} : Cap{chunk, 0.0f, 0.0f};
+}
+
+int prefill_launch(const void* q, const void* k_cache, const void* v_cache, void* out,
                                         const int* block_table, const int* q_start, const int* kv_len,
                                         int n_seqs, int max_q_len, int nh, int nkv, int hd, int page_size,
-                                        int max_pages, int window, float scale, cudaStream_t stream) {
+                                        int max_pages, int window, float scale, const Cap& cap, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return 0;
   JB_REFUSE(hd != HD, "attention_bf16: built for head_dim %d, called with %d", HD, hd);
   JB_REFUSE(page_size != PAGE, "attention_bf16: page size %d (need %d)", page_size, PAGE);
@@ -631,7 +650,27 @@ JB_EXPORT int jb_attention_bf16_prefill(const void* q, const void* k_cache, cons
   jb::Launch cfg(grid, dim3(THREADS), PREFILL_SMEM, stream);
   return (int)cudaLaunchKernelEx(&cfg.c, prefill_kernel, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                                  (bf16*)out, block_table, q_start, kv_len, nh, nkv, max_pages, window,
-                                 scale * LOG2E);
+                                 scale * LOG2E, cap);
+}
+}  // namespace
+
+JB_EXPORT int jb_attention_bf16_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                        const int* block_table, const int* q_start, const int* kv_len,
+                                        int n_seqs, int max_q_len, int nh, int nkv, int hd, int page_size,
+                                        int max_pages, int window, float scale, cudaStream_t stream) {
+  return prefill_launch(q, k_cache, v_cache, out, block_table, q_start, kv_len, n_seqs, max_q_len, nh, nkv, hd,
+                        page_size, max_pages, window, scale, Cap{0, 0.0f, 0.0f}, stream);
+}
+
+// As jb_attention_bf16_prefill, with a chunked mask (chunk > 0: a query sees only the keys of its own chunk of
+// positions) and capped scores (softcap > 0: s -> softcap tanh(s / softcap)).
+JB_EXPORT int jb_attention_bf16_prefill_capped(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                               const int* block_table, const int* q_start, const int* kv_len,
+                                               int n_seqs, int max_q_len, int nh, int nkv, int hd, int page_size,
+                                               int max_pages, int window, float scale, int chunk, float softcap,
+                                               cudaStream_t stream) {
+  return prefill_launch(q, k_cache, v_cache, out, block_table, q_start, kv_len, n_seqs, max_q_len, nh, nkv, hd,
+                        page_size, max_pages, window, scale, make_cap(chunk, softcap, scale), stream);
 }
 
 // Scratch (when n_splits > 1): part_o float32 [n_seqs * nh * n_splits * hd], part_ml float32
@@ -640,7 +679,7 @@ namespace {
 int decode_launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
                   const int* block_table, const int* kv_len, int n_seqs, int nh, int nkv, int hd, int page_size,
                   int max_pages, int window, float scale, int n_splits, const FusedInput& fused,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const Cap& cap = Cap{0, 0.0f, 0.0f}) {
   if (n_seqs <= 0) return 0;
   JB_REFUSE(hd != HD, "attention_bf16: built for head_dim %d, called with %d", HD, hd);
   JB_REFUSE(page_size != PAGE, "attention_bf16: page size %d (need %d)", page_size, PAGE);
@@ -651,7 +690,7 @@ int decode_launch(const void* q, const void* k_cache, const void* v_cache, void*
   dim3 grid(n_seqs, nkv * n_rb, n_splits);
   cudaError_t le = decode_dispatch(grid, stream, true, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                                    (bf16*)out, part_o, part_ml, block_table, kv_len, nh, nkv, max_pages, window,
-                                   scale * LOG2E, n_splits, fused);
+                                   scale * LOG2E, n_splits, fused, cap);
   if (le != cudaSuccess) return (int)le;
   if (n_splits > 1) {
     jb::Launch cfg2(dim3(n_seqs * nh), dim3(HD >= 128 ? 128 : 64), 0, stream);
@@ -670,6 +709,17 @@ JB_EXPORT int jb_attention_bf16_decode(const void* q, const void* k_cache, const
                                        cudaStream_t stream) {
   return decode_launch(q, k_cache, v_cache, out, part_o, part_ml, block_table, kv_len, n_seqs, nh, nkv, hd,
                        page_size, max_pages, window, scale, n_splits, FusedInput{}, stream);
+}
+
+// As jb_attention_bf16_decode, with a chunked mask and capped scores (see jb_attention_bf16_prefill_capped).
+JB_EXPORT int jb_attention_bf16_decode_capped(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                              float* part_o, float* part_ml, const int* block_table,
+                                              const int* kv_len, int n_seqs, int nh, int nkv, int hd, int page_size,
+                                              int max_pages, int window, float scale, int n_splits, int chunk,
+                                              float softcap, cudaStream_t stream) {
+  return decode_launch(q, k_cache, v_cache, out, part_o, part_ml, block_table, kv_len, n_seqs, nh, nkv, hd,
+                       page_size, max_pages, window, scale, n_splits, FusedInput{}, stream,
+                       make_cap(chunk, softcap, scale));
 }
 
 // As jb_attention_bf16_decode, but q, k and v of the new tokens come as the projection's float32

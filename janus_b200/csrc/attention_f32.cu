@@ -1,6 +1,8 @@
 // Float32 grouped-query attention over the paged cache, for prefill and decode
 // alike: one warp per (token, query head); the token attends to the keys of
-// its own sequence at positions [max(0, pos-window+1), pos] (window 0 = all).
+// its own sequence at positions [max(0, pos-window+1), pos] (window 0 = all);
+// with chunk > 0 only to those of them that lie in its own chunk of positions,
+// [floor(pos/chunk) chunk, pos]; with softcap > 0 a score s becomes softcap tanh(s/softcap).
 // Formulas: crates/janus-engine/src/compute/shaders/attention.wgsl:96-115
 // (kv head = h*nkv/nh, score = dot * scale), softmax.wgsl:29-50 (exp(s-max)/sum),
 // attention.wgsl:170-185 (sum of p*v).  The softmax runs online over chunks of
@@ -25,7 +27,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_f32_kernel(
     const float* __restrict__ q, const float* __restrict__ k_cache, const float* __restrict__ v_cache,
     float* __restrict__ out, const int* __restrict__ block_table, const int* __restrict__ token_slot,
     const int* __restrict__ positions, int T, int nh, int nkv, int hd, int page_size, int max_pages,
-    int window, float scale) {
+    int window, float scale, int chunk, float softcap) {
   __shared__ __align__(16) float q_s[WARPS][MAX_HD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -34,7 +36,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_f32_kernel(
   const int kvh = (h * nkv) / nh;
   const int pos = positions[t];
   const int* pages = block_table + (size_t)token_slot[t] * max_pages;
-  const int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  int kstart = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (chunk > 0) kstart = max(kstart, (pos / chunk) * chunk);   // only the keys of the query's own chunk of positions
 
   const float* qv = q + ((size_t)t * nh + h) * hd;
   for (int d = lane; d < hd; d += 32) q_s[warp][d] = qv[d];
@@ -69,6 +72,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_f32_kernel(
         for (int d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], kr[d], dot);
       }
       s = dot * scale;
+      if (softcap > 0.0f) s = softcap * tanhf(s / softcap);
     }
     const float m_new = fmaxf(m, jb::warp_max(s));
     const float p = valid ? expf(s - m_new) : 0.0f;
@@ -118,7 +122,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_f32_kernel(
 JB_EXPORT int jb_attention_f32(const float* q, const float* k_cache, const float* v_cache, float* out,
                                const int* block_table, const int* token_slot, const int* positions, int T,
                                int nh, int nkv, int hd, int page_size, int max_pages, int window, float scale,
-                               cudaStream_t stream) {
+                               int chunk, float softcap, cudaStream_t stream) {
   if (T <= 0) return 0;
   JB_REFUSE(hd > MAX_HD || hd <= 0, "attention_f32: head_dim %d is outside (0, %d]", hd, MAX_HD);
   JB_REFUSE(nkv <= 0 || nh % nkv != 0, "attention_f32: %d heads are not a multiple of %d kv heads", nh, nkv);
@@ -127,11 +131,11 @@ JB_EXPORT int jb_attention_f32(const float* q, const float* k_cache, const float
   if (hd % 4 == 0 && (((uintptr_t)k_cache) & 15) == 0)
     attention_f32_kernel<true><<<blocks, WARPS * 32, 0, stream>>>(q, k_cache, v_cache, out, block_table, token_slot,
                                                                   positions, T, nh, nkv, hd, page_size, max_pages,
-                                                                  window, scale);
+                                                                  window, scale, chunk, softcap);
   else
     attention_f32_kernel<false><<<blocks, WARPS * 32, 0, stream>>>(q, k_cache, v_cache, out, block_table, token_slot,
                                                                    positions, T, nh, nkv, hd, page_size, max_pages,
-                                                                   window, scale);
+                                                                   window, scale, chunk, softcap);
   JB_CHECK_LAUNCH();
   return 0;
 }

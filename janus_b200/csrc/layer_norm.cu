@@ -1,0 +1,202 @@
+// What happens where a sublayer's output joins the residual stream and the next sublayer reads it, in one launch,
+// for designs with a layer norm (or a root-mean-square norm), a per-feature scale on what joins the stream, and
+// sublayers made of two branches.  All arithmetic is float32.  For one row r of the stream (width W):
+//
+//   y  = ya                                                     (a sublayer's output), or, with branch weights,
+//   y  = mult (ya / rms(ya) wa + yb / rms(yb) wb)               rms(v) = sqrt(mean(v^2) + eps)
+//   r <- r + scale * y          (scale per feature, or 1)       ya and yb are set to zero afterwards
+//   r <- r + extra              (another stream's row, e.g. the embedding's output that joins before a pass)
+//   x  = (r - mean(r)) / sqrt(mean((r - mean(r))^2) + eps) gamma        (center = 1: layer norm, no bias)
+//   x  = r / sqrt(mean(r^2) + eps) gamma                                (center = 0)
+//
+// Every step is optional: without ya the row is only read; without gamma nothing is normed; with row_index the
+// rows of x are picked (x[i] = norm(r[row_index[i]])) and the stream is not written.  `clear`, `clear2`: float32
+// buffers of whole 16-byte vectors that the launch sets to zero on the way.  One block per row; the row lives in
+// shared memory between the passes.
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void clear_slice(float4* buf, size_t n4) {
+  if (buf == nullptr) return;
+  const float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) buf[i] = z;
+}
+
+template <typename TO>
+__global__ void join_norm_kernel(float* __restrict__ stream, float* __restrict__ ya, float* __restrict__ yb,
+                                 const float* __restrict__ wa, const float* __restrict__ wb, float mult,
+                                 const float* __restrict__ scale, const float* __restrict__ extra,
+                                 const float* __restrict__ gamma, float eps, int center, TO* __restrict__ x_out,
+                                 const int* __restrict__ row_index, int W, float4* __restrict__ clear, size_t clear_n4,
+                                 float4* __restrict__ clear2, size_t clear2_n4) {
+  extern __shared__ __align__(16) float row_s[];   // the row of the stream
+  __shared__ float scratch[33];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  clear_slice(clear, clear_n4);
+  clear_slice(clear2, clear2_n4);
+  const size_t src = row_index != nullptr ? (size_t)row_index[blockIdx.x] : (size_t)blockIdx.x;
+  float* r = stream + src * W;
+  float inv_a = 1.0f, inv_b = 1.0f;
+  if (ya != nullptr && wa != nullptr) {
+    float sa = 0.0f, sb = 0.0f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float a = ya[src * W + i], b = yb[src * W + i];
+      sa = fmaf(a, a, sa);
+      sb = fmaf(b, b, sb);
+    }
+    sa = jb::block_sum(sa, scratch);
+    sb = jb::block_sum(sb, scratch);
+    inv_a = 1.0f / sqrtf(sa / (float)W + eps);
+    inv_b = 1.0f / sqrtf(sb / (float)W + eps);
+  }
+  float sum = 0.0f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = r[i];
+    if (ya != nullptr) {
+      float y = ya[src * W + i];
+      ya[src * W + i] = 0.0f;
+      if (wa != nullptr) {
+        y = mult * ((y * inv_a) * wa[i] + (yb[src * W + i] * inv_b) * wb[i]);
+        yb[src * W + i] = 0.0f;
+      }
+      v = scale != nullptr ? fmaf(scale[i], y, v) : v + y;
+    }
+    if (extra != nullptr) v += extra[src * W + i];
+    if (ya != nullptr || extra != nullptr) r[i] = v;
+    row_s[i] = v;
+    sum += v;
+  }
+  if (x_out == nullptr) return;
+  float mean = 0.0f;
+  if (center) mean = jb::block_sum(sum, scratch) / (float)W;
+  float sq = 0.0f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {   // a thread reads back what it wrote itself
+    const float d = row_s[i] - mean;
+    sq = fmaf(d, d, sq);
+  }
+  sq = jb::block_sum(sq, scratch);
+  const float inv = 1.0f / sqrtf(sq / (float)W + eps);
+  TO* x = x_out + (size_t)blockIdx.x * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) x[i] = jb::from_f32<TO>(((row_s[i] - mean) * inv) * gamma[i]);
+}
+
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * act(gate[t, h, :]), one warp per (token, head);
+// weight [e] is shared by the heads; act: 0 = SiLU, 1 = sigmoid.
+template <typename TO>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate, int ld_gate,
+                                      const float* __restrict__ weight, float eps, int act, TO* __restrict__ out,
+                                      long long items, int heads, int e) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = item / heads;
+  const int h = (int)(item % heads);
+  const float* row = o + (size_t)item * e;
+  float ss = 0.0f;
+  for (int i = lane; i < e; i += 32) ss = fmaf(row[i], row[i], ss);
+  ss = jb::warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)e + eps);
+  const float* g = gate + (size_t)t * ld_gate + (size_t)h * e;
+  for (int i = lane; i < e; i += 32) {
+    const float z = g[i], s = 1.0f / (1.0f + expf(-z));
+    out[(size_t)item * e + i] = jb::from_f32<TO>(((row[i] * inv) * weight[i]) * (act == 0 ? z * s : s));
+  }
+}
+
+// x[t, h, j] *= sigmoid(gate[t, h e + j]) for j < e, in place: x holds heads of `stored` >= e numbers (the columns
+// behind e are left alone), the gate is float32 with rows of ld_gate floats.
+template <typename TO>
+__global__ void sigmoid_gate_kernel(TO* __restrict__ x, const float* __restrict__ gate, int ld_gate, int heads, int e,
+                                    int stored, long long n) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int j = (int)(i % stored);
+    if (j >= e) continue;
+    const long long th = i / stored;
+    const long long t = th / heads;
+    const int h = (int)(th % heads);
+    const float z = gate[(size_t)t * ld_gate + (size_t)h * e + j];
+    x[i] = jb::from_f32<TO>(jb::to_f32(x[i]) / (1.0f + expf(-z)));
+  }
+}
+
+}  // namespace
+
+// stream: float32 [rows of the stream, W]; ya, yb: float32 of the stream's shape or null; wa, wb, scale, gamma: float32 [W]
+// or null; extra: float32 of the stream's shape or null; x_out: [T, W] in out_dtype or null; row_index: int32 [T] or null.
+JB_EXPORT int jb_join_norm(float* stream, float* ya, float* yb, const float* wa, const float* wb, float mult,
+                           const float* scale, const float* extra, const float* gamma, float eps, int center,
+                           void* x_out, int out_dtype, const int* row_index, int T, int W, float* clear,
+                           long long clear_n, float* clear2, long long clear2_n, cudaStream_t stream_) {
+  if (T <= 0) return 0;
+  JB_REFUSE((clear != nullptr && ((clear_n & 3) != 0 || ((uintptr_t)clear & 15) != 0)) ||
+                (clear2 != nullptr && ((clear2_n & 3) != 0 || ((uintptr_t)clear2 & 15) != 0)),
+            "join_norm: a buffer to clear is not made of whole 16-byte vectors");
+  JB_REFUSE((wa != nullptr) != (wb != nullptr) || (wa != nullptr && (ya == nullptr || yb == nullptr)),
+            "join_norm: two branches need two outputs and two weights");
+  JB_REFUSE(row_index != nullptr && (ya != nullptr || extra != nullptr), "join_norm: picked rows are only read");
+  JB_REFUSE(x_out != nullptr && gamma == nullptr, "join_norm: a norm needs its weight");
+  const size_t smem = (size_t)W * sizeof(float);
+  JB_REFUSE(smem > 200 * 1024, "join_norm: a row of %d floats does not fit shared memory", W);
+  jb::Launch cfg(dim3(T), dim3(W >= 2048 ? 512 : W >= 512 ? 256 : 128), smem, stream_);
+  cudaError_t e;
+#define JB_LAUNCH_JN(TO)                                                                                           \
+  do {                                                                                                             \
+    if (smem > 48 * 1024) {                                                                                        \
+      e = cudaFuncSetAttribute(join_norm_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+      if (e != cudaSuccess) return (int)e;                                                                         \
+    }                                                                                                              \
+    e = cudaLaunchKernelEx(&cfg.c, join_norm_kernel<TO>, stream, ya, yb, wa, wb, mult, scale, extra, gamma, eps,   \
+                           center, (TO*)x_out, row_index, W, (float4*)clear, clear ? (size_t)clear_n >> 2 : (size_t)0, \
+                           (float4*)clear2, clear2 ? (size_t)clear2_n >> 2 : (size_t)0);                           \
+  } while (0)
+  if (out_dtype == JB_F32) JB_LAUNCH_JN(float);
+  else if (out_dtype == JB_BF16) JB_LAUNCH_JN(bf16);
+  else return JB_ERR_BAD_DTYPE;
+#undef JB_LAUNCH_JN
+  return (int)e;
+}
+
+// o: float32 [T, heads e]; gate: float32 rows of ld_gate floats, head h at columns [h e, (h + 1) e); weight float32 [e].
+JB_EXPORT int jb_head_norm_gate(const float* o, const float* gate, int ld_gate, const float* weight, float eps, int act,
+                                void* out, int out_dtype, int T, int heads, int e, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const long long items = (long long)T * heads;
+  jb::Launch cfg(dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream);
+  cudaError_t err;
+  if (out_dtype == JB_F32)
+    err = cudaLaunchKernelEx(&cfg.c, head_norm_gate_kernel<float>, o, gate, ld_gate, weight, eps, act, (float*)out, items,
+                             heads, e);
+  else if (out_dtype == JB_BF16)
+    err = cudaLaunchKernelEx(&cfg.c, head_norm_gate_kernel<bf16>, o, gate, ld_gate, weight, eps, act, (bf16*)out, items,
+                             heads, e);
+  else
+    return JB_ERR_BAD_DTYPE;
+  return (int)err;
+}
+
+// x: [T, heads stored] in dtype; gate: float32 rows of ld_gate floats, head h at columns [h e, (h + 1) e).
+JB_EXPORT int jb_sigmoid_gate(void* x, int dtype, const float* gate, int ld_gate, int T, int heads, int e, int stored,
+                              cudaStream_t stream) {
+  if (T <= 0 || heads <= 0) return 0;
+  JB_REFUSE(stored < e, "sigmoid_gate: heads of %d cannot be stored in %d columns", e, stored);
+  const long long n = (long long)T * heads * stored;
+  jb::Launch cfg(dim3((unsigned)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096)), dim3(256), 0, stream);
+  cudaError_t err;
+  if (dtype == JB_F32)
+    err = cudaLaunchKernelEx(&cfg.c, sigmoid_gate_kernel<float>, (float*)x, gate, ld_gate, heads, e, stored, n);
+  else if (dtype == JB_BF16)
+    err = cudaLaunchKernelEx(&cfg.c, sigmoid_gate_kernel<bf16>, (bf16*)x, gate, ld_gate, heads, e, stored, n);
+  else
+    return JB_ERR_BAD_DTYPE;
+  return (int)err;
+}

@@ -115,6 +115,69 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int ld, int Q
   for (int i = threadIdx.x; i < r; i += blockDim.x) out[i] = jb::from_f32<TO>((pr[Q + i] / rms) * w[i]);
 }
 
+// head_norm_rope_cache (grouped-query attention whose queries and keys are normed head by head):
+//   q = proj[:, 0 : H d], k = proj[:, H d : (H + G) d], v = proj[:, (H + G) d : (H + G) d + G e]
+//   every head of q and of k is divided by its own root mean square over d (eps inside the root) and multiplied by
+//   wq (or wk), a weight of size d that all heads share (null: no norm); then the first `rot` dimensions are turned
+//   as above.  q is written [T, H dp], k and v are appended to pages whose rows hold dp numbers (dp >= d, dp >= e; the
+//   extra columns of q are zero, those of the pages are never written).  One block per token, a warp per head.
+template <typename TO>
+__global__ void head_norm_rope_cache_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ wq,
+                                            const float* __restrict__ wk, float eps, const float* __restrict__ table,
+                                            int rot, const int* __restrict__ positions, TO* __restrict__ q_out,
+                                            const int* __restrict__ dest, TO* __restrict__ k_cache,
+                                            TO* __restrict__ v_cache, int H, int G, int d, int e, int dp, int page_size,
+                                            int write_kv) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const float* pr = proj + (size_t)t * ld;
+  size_t page = 0;
+  int prow = 0;
+  if (write_kv) {
+    page = (size_t)(dest[t] / page_size);
+    prow = dest[t] % page_size;
+  }
+  const int half = rot >> 1;
+  const float* cs = (table != nullptr && rot > 0) ? table + (size_t)positions[t] * half * 2 : nullptr;
+  const int n_heads = H + (write_kv ? 2 * G : 0);
+  for (int head = warp; head < n_heads; head += warps) {
+    if (head >= H + G) {                                // a value head: appended as projected
+      const int g = head - H - G;
+      const float* x = pr + (size_t)(H + G) * d + (size_t)g * e;
+      TO* out = v_cache + ((page * G + g) * page_size + prow) * dp;
+      for (int j = lane; j < e; j += 32) out[j] = jb::from_f32<TO>(x[j]);
+      continue;
+    }
+    const bool is_q = head < H;
+    const float* x = pr + (size_t)head * d;
+    const float* w = is_q ? wq : wk;
+    float inv = 1.0f;
+    if (w != nullptr) {
+      float ss = 0.0f;
+      for (int j = lane; j < d; j += 32) ss = fmaf(x[j], x[j], ss);
+      ss = jb::warp_sum(ss);
+      inv = 1.0f / sqrtf(ss / (float)d + eps);
+    }
+    TO* out = is_q ? q_out + ((size_t)t * H + head) * dp
+                   : k_cache + ((page * G + (head - H)) * page_size + prow) * dp;
+    for (int j = lane; j < d; j += 32) {
+      if (cs != nullptr && j < rot) {
+        if (j >= half) continue;                        // written with the pair's first member
+        const float u = (x[j] * inv) * (w ? w[j] : 1.0f), v = (x[j + half] * inv) * (w ? w[j + half] : 1.0f);
+        const float co = cs[2 * j], si = cs[2 * j + 1];
+        out[j] = jb::from_f32<TO>(u * co - v * si);
+        out[j + half] = jb::from_f32<TO>(v * co + u * si);
+      } else {
+        out[j] = jb::from_f32<TO>((x[j] * inv) * (w ? w[j] : 1.0f));
+      }
+    }
+    if (is_q)
+      for (int j = d + lane; j < dp; j += 32) out[j] = jb::from_f32<TO>(0.0f);
+  }
+}
+
 }  // namespace
 
 // proj: float32 [T, ld]; bq [H d], bk [G d] (either may be null), wq [H d], wk [G d] float32; table: float32
@@ -166,4 +229,28 @@ JB_EXPORT int jb_latent_prep(const float* proj, int ld, int Q, int r, int rp, co
   else
     return JB_ERR_BAD_DTYPE;
   return (int)e;
+}
+
+// proj: float32 [T, ld] = [q: H d | k: G d | v: G e]; wq, wk: float32 [d] or null; table: float32 [positions][rot/2][2]
+// or null; q_out [T, H dp] and the pages (rows of dp) in out_dtype.  write_kv = 0: q only.
+JB_EXPORT int jb_head_norm_rope_cache(const float* proj, int ld, const float* wq, const float* wk, float eps,
+                                      const float* table, int rot, const int* positions, void* q_out, int out_dtype,
+                                      const int* dest, void* k_cache, void* v_cache, int T, int H, int G, int d, int e,
+                                      int dp, int page_size, int write_kv, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  JB_REFUSE(dp < d || dp < e, "head_norm_rope_cache: heads of %d and %d cannot be stored in %d columns", d, e, dp);
+  JB_REFUSE(rot < 0 || rot > d || (rot & 1), "head_norm_rope_cache: %d rotated dimensions do not fit a head of %d", rot, d);
+  JB_REFUSE(ld < H * d + (write_kv ? G * (d + e) : 0), "head_norm_rope_cache: rows of %d floats do not hold the projections", ld);
+  const int heads = H + (write_kv ? 2 * G : 0);
+  jb::Launch cfg(dim3(T), dim3(heads >= 8 ? 256 : heads >= 4 ? 128 : 64), 0, stream);
+  cudaError_t err;
+  if (out_dtype == JB_F32)
+    err = cudaLaunchKernelEx(&cfg.c, head_norm_rope_cache_kernel<float>, proj, ld, wq, wk, eps, table, rot, positions,
+                             (float*)q_out, dest, (float*)k_cache, (float*)v_cache, H, G, d, e, dp, page_size, write_kv);
+  else if (out_dtype == JB_BF16)
+    err = cudaLaunchKernelEx(&cfg.c, head_norm_rope_cache_kernel<bf16>, proj, ld, wq, wk, eps, table, rot, positions,
+                             (bf16*)q_out, dest, (bf16*)k_cache, (bf16*)v_cache, H, G, d, e, dp, page_size, write_kv);
+  else
+    return JB_ERR_BAD_DTYPE;
+  return (int)err;
 }

@@ -1,0 +1,289 @@
+// A feed-forward made of experts of which every token uses a few: the router's choice, the experts' products for
+// steps of few tokens (every chosen expert's rows are streamed once per token that chose it, float32 sums), and the
+// bookkeeping around the tensor-core products of steps with many tokens (rows gathered expert by expert, results
+// added back token by token).
+//
+//   scores s = sigmoid(z) of the router's float32 logits z [T, E]; a token's `top` experts are those with the largest
+//   scores (the lower index wins a tie); its weights are those scores, as they are.
+//   out[t] += sum over the chosen e of  Wd_e ( act(Wg_e x) * (Wu_e x) ),  x = s_e h[t]        (the weight is on the input)
+//
+// Experts' weights: gate and up [E][F][W], down [E][W][F], row-major, float32 or bfloat16.
+#include <math_constants.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+constexpr int MAX_TOP = 16;
+
+// one warp per token
+__global__ void route_topk_kernel(const float* __restrict__ logits, int ld, int E, int top, int* __restrict__ sel_e,
+                                  float* __restrict__ sel_w, int T) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const float* z = logits + (size_t)t * ld;
+  int picked[MAX_TOP];
+  for (int k = 0; k < top; ++k) {
+    float best = -CUDART_INF_F;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      bool taken = false;
+      for (int q = 0; q < k; ++q) taken |= picked[q] == e;
+      const float v = z[e];            // the sigmoid keeps the order of the logits
+      if (!taken && (v > best || (v == best && e < arg))) {
+        best = v;
+        arg = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) {
+        best = ob;
+        arg = oa;
+      }
+    }
+    picked[k] = arg;
+    if (lane == 0) {
+      sel_e[(size_t)t * top + k] = arg;
+      sel_w[(size_t)t * top + k] = 1.0f / (1.0f + expf(-best));
+    }
+  }
+}
+
+template <typename TW> struct Vec;
+template <> struct Vec<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float (&v)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  }
+};
+template <> struct Vec<bf16> {
+  static constexpr int N = 8;
+  __device__ static void load(const bf16* p, float (&v)[8]) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+
+constexpr int GU_WARPS = 8, GU_ROWS = 2;   // rows of gate (and of up) per warp
+
+// act[pair][f] = gated(Wg_e[f] . x, Wu_e[f] . x) with x = weight[pair] * h[token of the pair]
+template <typename TW, typename TX, bool VEC>
+__global__ void __launch_bounds__(GU_WARPS * 32) expert_gate_up_kernel(
+    const TX* __restrict__ h, const int* __restrict__ sel_e, const float* __restrict__ sel_w, int top,
+    const TW* __restrict__ w_gate, const TW* __restrict__ w_up, float* __restrict__ act, int W, int F, jb::Gate gate) {
+  extern __shared__ __align__(16) float x_s[];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int pair = blockIdx.y, t = pair / top;
+  const int e = sel_e[pair];
+  const float s = sel_w[pair];
+  for (int i = threadIdx.x; i < W; i += blockDim.x) x_s[i] = s * jb::to_f32(h[(size_t)t * W + i]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int f0 = (blockIdx.x * GU_WARPS + warp) * GU_ROWS;
+  if (f0 >= F) return;
+  const TW* g_rows = w_gate + ((size_t)e * F + f0) * W;
+  const TW* u_rows = w_up + ((size_t)e * F + f0) * W;
+  float ag[GU_ROWS], au[GU_ROWS];
+#pragma unroll
+  for (int r = 0; r < GU_ROWS; ++r) ag[r] = au[r] = 0.0f;
+  if (VEC) {
+    constexpr int N = Vec<TW>::N;
+    for (int i = lane * N; i < W; i += 32 * N) {
+      float gv[GU_ROWS][N], uv[GU_ROWS][N];
+#pragma unroll
+      for (int r = 0; r < GU_ROWS; ++r) {
+        const size_t off = (size_t)(f0 + r < F ? r : 0) * W + i;
+        Vec<TW>::load(g_rows + off, gv[r]);
+        Vec<TW>::load(u_rows + off, uv[r]);
+      }
+#pragma unroll
+      for (int q = 0; q < N; ++q) {
+        const float x = x_s[i + q];
+#pragma unroll
+        for (int r = 0; r < GU_ROWS; ++r) {
+          ag[r] = fmaf(gv[r][q], x, ag[r]);
+          au[r] = fmaf(uv[r][q], x, au[r]);
+        }
+      }
+    }
+  } else {
+    for (int i = lane; i < W; i += 32) {
+      const float x = x_s[i];
+#pragma unroll
+      for (int r = 0; r < GU_ROWS; ++r) {
+        const size_t off = (size_t)(f0 + r < F ? r : 0) * W + i;
+        ag[r] = fmaf(jb::to_f32(g_rows[off]), x, ag[r]);
+        au[r] = fmaf(jb::to_f32(u_rows[off]), x, au[r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < GU_ROWS; ++r) {
+    const float g = jb::warp_sum(ag[r]), u = jb::warp_sum(au[r]);
+    if (lane == 0 && f0 + r < F) act[(size_t)pair * F + f0 + r] = jb::gated(g, u, gate);
+  }
+}
+
+constexpr int DN_WARPS = 8, DN_ROWS = 4;
+
+// out[token of the pair][c] += Wd_e[c] . act[pair]
+template <typename TW, bool VEC>
+__global__ void __launch_bounds__(DN_WARPS * 32) expert_down_kernel(
+    const float* __restrict__ act, const int* __restrict__ sel_e, int top, const TW* __restrict__ w_down,
+    float* __restrict__ out, int W, int F) {
+  extern __shared__ __align__(16) float a_s[];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int pair = blockIdx.y, t = pair / top;
+  const int e = sel_e[pair];
+  for (int i = threadIdx.x; i < F; i += blockDim.x) a_s[i] = act[(size_t)pair * F + i];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c0 = (blockIdx.x * DN_WARPS + warp) * DN_ROWS;
+  if (c0 >= W) return;
+  const TW* rows = w_down + ((size_t)e * W + c0) * F;
+  float acc[DN_ROWS];
+#pragma unroll
+  for (int r = 0; r < DN_ROWS; ++r) acc[r] = 0.0f;
+  if (VEC) {
+    constexpr int N = Vec<TW>::N;
+    for (int i = lane * N; i < F; i += 32 * N) {
+      float wv[DN_ROWS][N];
+#pragma unroll
+      for (int r = 0; r < DN_ROWS; ++r) Vec<TW>::load(rows + (size_t)(c0 + r < W ? r : 0) * F + i, wv[r]);
+#pragma unroll
+      for (int q = 0; q < N; ++q) {
+        const float a = a_s[i + q];
+#pragma unroll
+        for (int r = 0; r < DN_ROWS; ++r) acc[r] = fmaf(wv[r][q], a, acc[r]);
+      }
+    }
+  } else {
+    for (int i = lane; i < F; i += 32) {
+      const float a = a_s[i];
+#pragma unroll
+      for (int r = 0; r < DN_ROWS; ++r)
+        acc[r] = fmaf(jb::to_f32(rows[(size_t)(c0 + r < W ? r : 0) * F + i]), a, acc[r]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < DN_ROWS; ++r) {
+    const float v = jb::warp_sum(acc[r]);
+    if (lane == 0 && c0 + r < W) {
+      if (top == 1) out[(size_t)t * W + c0 + r] += v;      // the token's only pair: nobody else adds here
+      else atomicAdd(out + (size_t)t * W + c0 + r, v);
+    }
+  }
+}
+
+// rows[i] = weight[order[i]] * h[order[i] / top] in the products' dtype: the pairs (token, choice) in the order the
+// experts' products take them
+template <typename TX>
+__global__ void expert_gather_kernel(const TX* __restrict__ h, const int* __restrict__ order,
+                                     const float* __restrict__ sel_w, int top, TX* __restrict__ rows, int W) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int pair = order[blockIdx.x];
+  const float s = sel_w[pair];
+  const TX* src = h + (size_t)(pair / top) * W;
+  TX* dst = rows + (size_t)blockIdx.x * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = jb::from_f32<TX>(s * jb::to_f32(src[i]));
+}
+
+// out[t] += sum over k of results[where[t * top + k]]
+__global__ void expert_scatter_kernel(const float* __restrict__ results, const int* __restrict__ where, int top,
+                                      float* __restrict__ out, int W) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = 0.0f;
+    for (int k = 0; k < top; ++k) v += results[(size_t)where[(size_t)t * top + k] * W + i];
+    out[(size_t)t * W + i] += v;
+  }
+}
+
+template <typename T> bool aligned16(const T* p) { return ((uintptr_t)p & 15) == 0; }
+
+}  // namespace
+
+JB_EXPORT int jb_route_topk(const float* logits, int ld, int E, int top, int* sel_e, float* sel_w, int T,
+                            cudaStream_t stream) {
+  if (T <= 0) return 0;
+  JB_REFUSE(top < 1 || top > MAX_TOP || top > E, "route_topk: %d of %d experts (at most %d a token)", top, E, MAX_TOP);
+  jb::Launch cfg(dim3((T + 3) / 4), dim3(128), 0, stream);
+  return (int)cudaLaunchKernelEx(&cfg.c, route_topk_kernel, logits, ld, E, top, sel_e, sel_w, T);
+}
+
+// h: [T, W] in x_dtype; the experts' weights in w_dtype; act: float32 scratch [T top, F]; out: float32 [T, W], added to.
+JB_EXPORT int jb_experts_few_tokens(const void* h, int x_dtype, const int* sel_e, const float* sel_w, int top,
+                                    const void* w_gate, const void* w_up, const void* w_down, int w_dtype, float* act,
+                                    float* out, int T, int W, int F, float gate_limit, float gate_alpha,
+                                    cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int pairs = T * top;
+  JB_REFUSE((size_t)max(W, F) * sizeof(float) > 48 * 1024, "experts: rows of %d floats do not fit shared memory", max(W, F));
+  JB_REFUSE(pairs > 65535, "experts: %d (token, expert) pairs are too many for the few-token kernels", pairs);
+  const jb::Gate gate{gate_limit, gate_alpha};
+  jb::Launch c1(dim3((F + GU_WARPS * GU_ROWS - 1) / (GU_WARPS * GU_ROWS), pairs), dim3(GU_WARPS * 32),
+                (size_t)W * sizeof(float), stream);
+  jb::Launch c2(dim3((W + DN_WARPS * DN_ROWS - 1) / (DN_WARPS * DN_ROWS), pairs), dim3(DN_WARPS * 32),
+                (size_t)F * sizeof(float), stream);
+  cudaError_t e;
+#define JB_LAUNCH_EX(TW, TX)                                                                                          \
+  do {                                                                                                                \
+    const bool v1 = W % Vec<TW>::N == 0 && aligned16((const TW*)w_gate) && aligned16((const TW*)w_up);                \
+    const bool v2 = F % Vec<TW>::N == 0 && aligned16((const TW*)w_down);                                              \
+    e = v1 ? cudaLaunchKernelEx(&c1.c, expert_gate_up_kernel<TW, TX, true>, (const TX*)h, sel_e, sel_w, top,          \
+                                (const TW*)w_gate, (const TW*)w_up, act, W, F, gate)                                  \
+           : cudaLaunchKernelEx(&c1.c, expert_gate_up_kernel<TW, TX, false>, (const TX*)h, sel_e, sel_w, top,         \
+                                (const TW*)w_gate, (const TW*)w_up, act, W, F, gate);                                 \
+    if (e != cudaSuccess) return (int)e;                                                                              \
+    e = v2 ? cudaLaunchKernelEx(&c2.c, expert_down_kernel<TW, true>, (const float*)act, sel_e, top, (const TW*)w_down, \
+                                out, W, F)                                                                            \
+           : cudaLaunchKernelEx(&c2.c, expert_down_kernel<TW, false>, (const float*)act, sel_e, top,                  \
+                                (const TW*)w_down, out, W, F);                                                        \
+  } while (0)
+  if (w_dtype == JB_F32 && x_dtype == JB_F32) JB_LAUNCH_EX(float, float);
+  else if (w_dtype == JB_BF16 && x_dtype == JB_BF16) JB_LAUNCH_EX(bf16, bf16);
+  else return JB_ERR_BAD_DTYPE;
+#undef JB_LAUNCH_EX
+  return (int)e;
+}
+
+// rows: [pairs, W] in dtype, row i = weight[order[i]] * h[order[i] / top]
+JB_EXPORT int jb_expert_gather(const void* h, int dtype, const int* order, const float* sel_w, int top, void* rows,
+                               int pairs, int W, cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  jb::Launch cfg(dim3(pairs), dim3(W >= 1024 ? 256 : 128), 0, stream);
+  cudaError_t e;
+  if (dtype == JB_F32)
+    e = cudaLaunchKernelEx(&cfg.c, expert_gather_kernel<float>, (const float*)h, order, sel_w, top, (float*)rows, W);
+  else if (dtype == JB_BF16)
+    e = cudaLaunchKernelEx(&cfg.c, expert_gather_kernel<bf16>, (const bf16*)h, order, sel_w, top, (bf16*)rows, W);
+  else
+    return JB_ERR_BAD_DTYPE;
+  return (int)e;
+}
+
+// out[t] += sum_k results[where[t top + k]]; results float32 [pairs, W], out float32 [T, W]
+JB_EXPORT int jb_expert_scatter(const float* results, const int* where, int top, float* out, int T, int W,
+                                cudaStream_t stream) {
+  if (T <= 0) return 0;
+  jb::Launch cfg(dim3(T), dim3(W >= 1024 ? 256 : 128), 0, stream);
+  return (int)cudaLaunchKernelEx(&cfg.c, expert_scatter_kernel, results, where, top, out, W);
+}

@@ -99,6 +99,7 @@ class DecoderModel:
         T = ctx.n_tokens
         residual = ctx.workspace.get("residual", (T, self.streams * self.hidden_size), torch.float32)
         transforms = self.embedding_transforms
+        scale = None
         if self.streams == 1:
             # a single embedding transform that only multiplies is done by the gather itself
             scale = getattr(transforms[0], "plain_scale", lambda: None)() if len(transforms) == 1 else None
@@ -112,8 +113,25 @@ class DecoderModel:
                               ctx.seq_slot if ctx.feedback is not None else None)
         for transform in transforms:
             transform.forward(residual, ctx)
+        embedded = None
+        if any(e.adds_embedding for e in self.schedule):
+            # a copy of the embedding's output for the places that add it to the residual stream again
+            embedded = ctx.workspace.get("embedded", tuple(residual.shape), torch.float32)
+            if self.streams == 1 and not transforms:
+                ops.embed_gather(self.embedding, ctx.token_ids, embedded, ctx.feedback,
+                                 ctx.seq_slot if ctx.feedback is not None else None,
+                                 scale=1.0 if scale is None else scale)
+            else:
+                embedded.zero_()
+                ops.residual_add(embedded, residual)
         ctx.pending_write = None
         for place, entry in enumerate(self.schedule):
+            if entry.adds_embedding:
+                if ctx.pending_write is not None:       # the sum so far is complete before the embedding joins it
+                    connection, y = ctx.pending_write
+                    connection.write(residual, y)
+                    ctx.pending_write = None
+                ops.residual_add(residual, embedded)
             view = ctx.cache_view(place if entry.reads_cache_of is None else entry.reads_cache_of)
             with log.nvtx_range(f"place {place}: layer {entry.layer}"):
                 self.layers[entry.layer].forward(residual, ctx, view, writes_cache=entry.reads_cache_of is None)

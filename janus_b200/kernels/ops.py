@@ -56,12 +56,18 @@ _SIGNATURES = {
     "jb_embed_gather": "pippiippfp", "jb_rmsnorm": "pppifpiiiplp", "jb_residual_add": "ppilp",
     "jb_swiglu": "ppiiip", "jb_swiglu_f32_to_bf16": "piipiip", "jb_zero_f32": "plp",
     "jb_pack_weight_bf16": "piipp", "jb_rope_cache_write": "piipipppppiiiiiiip",
-    "jb_gemm_f32": "pppiiiiiip", "jb_attention_f32": "pppppppiiiiiiifp",
+    "jb_gemm_f32": "pppiiiiiip", "jb_attention_f32": "pppppppiiiiiiififp",
     "jb_gemm_bf16": "pplipiiiiiiplpiffpp", "jb_gemm_bf16_pair": "pplipiiiiiiiffpp",
     "jb_gemm_bf16_pair_qkv_rope": "ppliippppppiiiipp",
     "jb_sample": "piipfiffppupppp",
     "jb_attention_bf16_prefill": "pppppppiiiiiiiifp", "jb_attention_bf16_decode": "ppppppppiiiiiiifip",
     "jb_attention_bf16_decode_fused": "pipppppppppiiiiiiifiip",
+    "jb_attention_bf16_prefill_capped": "pppppppiiiiiiiififp", "jb_attention_bf16_decode_capped": "ppppppppiiiiiiifiifp",
+    "jb_join_norm": "pppppfpppfipipiiplplp", "jb_head_norm_gate": "ppipfipiiiip", "jb_sigmoid_gate": "pipiiiiip",
+    "jb_head_norm_rope_cache": "pippfpippipppiiiiiiiip",
+    "jb_delta_rule": "piiiipiiippfppllppiiiiip",
+    "jb_route_topk": "piiippip", "jb_experts_few_tokens": "pippipppippiiiffp", "jb_expert_gather": "pippipiip",
+    "jb_expert_scatter": "ppipiip",
     "jb_attention_tc_prefill": "pppppppiiiiiiiiiifpp",
     "jb_streams_rmsnorm": "pppipifpiiipplp", "jb_streams_mix": "ppppiiip", "jb_streams_mix_rmsnorm": "pppppipifpiiiplp", "jb_embed_streams": "pippiiippp",
     "jb_lightning_scan": "piiiipppppiiiiiipp", "jb_gated_rmsnorm": "ppipifpiiip",
@@ -284,7 +290,10 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, accumulate: bool
 
 def attention_f32(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                   block_table: torch.Tensor, token_slot: torch.Tensor, positions: torch.Tensor,
-                  nh: int, nkv: int, hd: int, page_size: int, window: int, scale: float) -> None:
+                  nh: int, nkv: int, hd: int, page_size: int, window: int, scale: float, chunk: int = 0,
+                  softcap: float = 0.0) -> None:
+    """`chunk` > 0: a query sees only the keys of its own chunk of positions, [floor(pos / chunk) chunk, pos];
+    `softcap` > 0: a score s becomes softcap tanh(s / softcap)."""
     T = q.shape[0]
     _need(q, "attention q", torch.float32, (T, nh * hd))
     _need(out, "attention out", torch.float32, (T, nh * hd))
@@ -295,7 +304,7 @@ def attention_f32(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     _need(positions, "positions", torch.int32, (T,))
     _check(_lib("attention_f32").jb_attention_f32(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(token_slot), _ptr(positions),
-        T, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale, _stream()),
+        T, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale, int(chunk), float(softcap), _stream()),
         "attention_f32")
 
 
@@ -725,9 +734,9 @@ def _attention_lib(hd: int):
 def attention_bf16_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                            block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor,
                            n_seqs: int, max_q_len: int, nh: int, nkv: int, hd: int, page_size: int,
-                           window: int, scale: float) -> None:
+                           window: int, scale: float, chunk: int = 0, softcap: float = 0.0) -> None:
     """Causal attention of each sequence's new tokens (the last q_len positions of
-    its kv_len) over its cached keys."""
+    its kv_len) over its cached keys.  `chunk`, `softcap`: as in `attention_f32`."""
     T = q.shape[0]
     _need(q, "attention q", torch.bfloat16, (T, nh * hd))
     _need(out, "attention out", torch.bfloat16, (T, nh * hd))
@@ -736,6 +745,12 @@ def attention_bf16_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     _need(block_table, "block table", torch.int32)
     _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
     _need(kv_len, "kv_len", torch.int32, (n_seqs,))
+    if chunk or softcap:
+        _check(_attention_lib(hd).jb_attention_bf16_prefill_capped(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
+            n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale, int(chunk),
+            float(softcap), _stream()), "attention_bf16_prefill")
+        return
     _check(_attention_lib(hd).jb_attention_bf16_prefill(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
         n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale,
@@ -819,8 +834,9 @@ def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_ca
                           page_size: int, window: int, scale: float, workspace, max_kv_len: int,
                           n_splits: Optional[int] = None, qkv: Optional[torch.Tensor] = None,
                           cos_sin: Optional[torch.Tensor] = None, dest: Optional[torch.Tensor] = None,
-                          write_kv: bool = True) -> None:
-    """One new token per sequence (its last position) over its cached keys.
+                          write_kv: bool = True, chunk: int = 0, softcap: float = 0.0) -> None:
+    """One new token per sequence (its last position) over its cached keys.  `chunk`, `softcap` (with `q` only): as
+    in `attention_f32`.
 
     Either `q` (rotated bf16 queries; the cache already holds the new token), or `qkv`: the
     projection's float32 output [B, (nh + 2 nkv) hd] (or [B, nh hd] with write_kv False), which the
@@ -842,11 +858,19 @@ def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_ca
     kernels = 2 if n_splits > 1 else 1
     if qkv is None:
         _need(q, "attention q", torch.bfloat16, (B, nh * hd))
+        if chunk or softcap:
+            _check(lib.jb_attention_bf16_decode_capped(
+                _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(block_table),
+                _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale,
+                int(n_splits), int(chunk), float(softcap), _stream()), "attention_bf16_decode", kernels=kernels)
+            return
         _check(lib.jb_attention_bf16_decode(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(block_table),
             _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale,
             int(n_splits), _stream()), "attention_bf16_decode", kernels=kernels)
         return
+    if chunk or softcap:
+        raise KernelError("attention decode: the kernel that rotates and appends takes no chunked mask and no cap")
     _need(qkv, "qkv", torch.float32)
     width = (nh + 2 * nkv) * hd if write_kv else nh * hd
     if qkv.shape[0] != B or qkv.shape[1] < width:
@@ -1345,3 +1369,180 @@ def gated_group_rmsnorm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tenso
     _check(_lib("mamba2").jb_gated_group_rmsnorm(
         _ptr(y), _ptr(gate), gate.stride(0), _ptr(weight), eps, _ptr(out), dtype_code(out.dtype), T, N, int(parts),
         _stream()), "gated_group_rmsnorm")
+
+
+# -- layer norm, scaled sums into the residual stream, sublayers of two branches ---------------------------------
+def join_norm(stream: torch.Tensor, ya: Optional[torch.Tensor] = None, yb: Optional[torch.Tensor] = None,
+              wa: Optional[torch.Tensor] = None, wb: Optional[torch.Tensor] = None, mult: float = 1.0,
+              scale: Optional[torch.Tensor] = None, extra: Optional[torch.Tensor] = None,
+              gamma: Optional[torch.Tensor] = None, eps: float = 0.0, center: bool = True,
+              x_out: Optional[torch.Tensor] = None, row_index: Optional[torch.Tensor] = None,
+              clear: Optional[torch.Tensor] = None, clear2: Optional[torch.Tensor] = None) -> None:
+    """One launch, row by row of the float32 stream r [T, W], every step optional:
+    y = ya, or with branch weights y = mult (ya / rms(ya) wa + yb / rms(yb) wb); r += scale * y (ya, yb set to zero);
+    r += extra; x_out = norm(r) * gamma (center: layer norm without bias, else root mean square), eps inside the
+    roots.  With `row_index` x_out's rows are norm(r[row_index[i]]) and r is only read.  `clear`, `clear2`: float32
+    scratch tensors (whole 16-byte vectors) set to zero on the way."""
+    W = stream.shape[1]
+    T = stream.shape[0] if row_index is None else row_index.shape[0]
+    _need(stream, "stream", torch.float32)
+    for t, name in ((ya, "sublayer output"), (yb, "second branch"), (extra, "stream to add")):
+        if t is not None:
+            _need(t, name, torch.float32, tuple(stream.shape))
+    for t, name in ((wa, "branch weight"), (wb, "branch weight"), (scale, "scale"), (gamma, "norm weight")):
+        if t is not None:
+            _need(t, name, torch.float32, (W,))
+    if x_out is not None:
+        _need(x_out, "normed rows", None, (T, W))
+    if row_index is not None:
+        _need(row_index, "row index", torch.int32)
+    for c in (clear, clear2):
+        if c is not None:
+            _need(c, "buffer to clear", torch.float32)
+    _check(_lib("layer_norm").jb_join_norm(
+        _ptr(stream), _ptr(ya), _ptr(yb), _ptr(wa), _ptr(wb), float(mult), _ptr(scale), _ptr(extra), _ptr(gamma),
+        float(eps), int(bool(center)), _ptr(x_out), dtype_code(x_out.dtype) if x_out is not None else F32,
+        _ptr(row_index), T, W, _ptr(clear), 0 if clear is None else clear.numel(), _ptr(clear2),
+        0 if clear2 is None else clear2.numel(), _stream()), "join_norm")
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                   heads: int, e: int, sigmoid: bool = False) -> None:
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * act(gate[t, h]) for float32 o [T, heads e], a float32
+    gate (a view whose rows may be wider) and a weight [e] that the heads share; act is SiLU, or the sigmoid."""
+    T = o.shape[0]
+    _need(o, "head outputs", torch.float32, (T, heads * e))
+    _need(weight, "head norm weight", torch.float32, (e,))
+    _need(out, "gated heads", None, (T, heads * e))
+    if gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape != o.shape:
+        raise KernelError("head_norm_gate: the gate must be float32 columns of the heads' shape")
+    _check(_lib("layer_norm").jb_head_norm_gate(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), float(eps),
+                                                1 if sigmoid else 0, _ptr(out), dtype_code(out.dtype), T, heads, e,
+                                                _stream()), "head_norm_gate")
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, heads: int, e: int, stored: int) -> None:
+    """x[t, h, j] *= sigmoid(gate[t, h, j]) in place for j < e; x [T, heads stored] holds heads of `stored` >= e numbers,
+    gate: float32 columns [T, heads e] (a view whose rows may be wider)."""
+    T = x.shape[0]
+    _need(x, "rows to gate", None, (T, heads * stored))
+    if gate.dtype != torch.float32 or gate.stride(1) != 1 or tuple(gate.shape) != (T, heads * e):
+        raise KernelError("sigmoid_gate: the gate must be float32 columns, one for each number of the heads")
+    _check(_lib("layer_norm").jb_sigmoid_gate(_ptr(x), dtype_code(x.dtype), _ptr(gate), gate.stride(0), T, heads, e,
+                                              stored, _stream()), "sigmoid_gate")
+
+
+def head_norm_rope_cache(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float,
+                         table: Optional[torch.Tensor], rot: int, positions: torch.Tensor, q_out: torch.Tensor,
+                         dest: Optional[torch.Tensor], k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                         heads: int, kv_heads: int, dim: int, vdim: int, stored_dim: int, page_size: int,
+                         write_kv: bool = True) -> None:
+    """proj float32 [T, >= heads dim + kv_heads (dim + vdim)]: q, k and v as projected.  Every head of q and k is
+    divided by its own root mean square and multiplied by the weight [dim] that the heads share (None: no norm), its
+    first `rot` dimensions are turned by the table's cos and sin at the token's position; q is written
+    [T, heads stored_dim], k and v are appended to pages whose rows hold stored_dim numbers."""
+    T = q_out.shape[0]
+    _need(proj, "projections", torch.float32)
+    if proj.shape[0] != T:
+        raise KernelError("head_norm_rope_cache: projections and queries differ in their rows")
+    _need(q_out, "q_out", None, (T, heads * stored_dim))
+    _need(positions, "positions", torch.int32, (T,))
+    for w in (wq, wk):
+        if w is not None:
+            _need(w, "head norm weight", torch.float32, (dim,))
+    if table is not None and rot > 0:
+        _need(table, "rotation table", torch.float32)
+        if tuple(table.shape[1:]) != (rot // 2, 2):
+            raise KernelError(f"head_norm_rope_cache: table of shape {tuple(table.shape)} does not fit {rot} dimensions")
+    if write_kv:
+        _need(dest, "cache rows", torch.int32, (T,))
+        _need(k_cache, "key pages", q_out.dtype)
+        _need(v_cache, "value pages", q_out.dtype)
+    _check(_lib("qk_prep").jb_head_norm_rope_cache(
+        _ptr(proj), proj.shape[1], _ptr(wq), _ptr(wk), float(eps), _ptr(table) if rot > 0 else None, int(rot),
+        _ptr(positions), _ptr(q_out), dtype_code(q_out.dtype), _ptr(dest) if write_kv else None,
+        _ptr(k_cache) if write_kv else None, _ptr(v_cache) if write_kv else None, T, heads, kv_heads, dim, vdim,
+        stored_dim, page_size, int(write_kv), _stream()), "head_norm_rope_cache")
+
+
+# -- the gated delta rule ------------------------------------------------------------------------------------------
+def delta_rule(conv: torch.Tensor, q_col: int, k_col: int, v_col: int, raw: torch.Tensor, b_col: int, a_col: int,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, unit_eps: float, out: torch.Tensor, state: torch.Tensor,
+               state_off: int, q_start: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int, heads: int, kv_heads: int,
+               dim: int, vdim: int) -> None:
+    """The recurrence S <- g S; w = beta (v - S^T k); S <- S + k w^T; o = S^T q per head, over each sequence's tokens
+    from the state its slot holds (float32 [slots, n], the [heads, dim, vdim] block at state_off), which is updated.
+    q, k (unit vectors are made here; q also times dim^-1/2) and v are columns of `conv`, beta's and the decay's
+    arguments columns of `raw`; g = exp(-exp(a_log) softplus(a + dt_bias)), beta = sigmoid(b)."""
+    T = conv.shape[0]
+    _need(conv, "convolved projections", torch.float32)
+    _need(raw, "projections", torch.float32)
+    _need(out, "recurrence out", torch.float32, (T, heads * vdim))
+    _need(a_log, "A_log", torch.float32, (heads,))
+    _need(dt_bias, "dt_bias", torch.float32, (heads,))
+    _need(state, "state", torch.float32)
+    if state.dim() != 2 or state_off + heads * dim * vdim > state.shape[1]:
+        raise KernelError("delta_rule: the state rows do not hold the recurrence's state")
+    _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
+    _need(seq_slot, "sequence slots", torch.int32, (n_seqs,))
+    _check(_lib("delta_rule").jb_delta_rule(
+        _ptr(conv), conv.shape[1], int(q_col), int(k_col), int(v_col), _ptr(raw), raw.shape[1], int(b_col), int(a_col),
+        _ptr(a_log), _ptr(dt_bias), float(unit_eps), _ptr(out), _ptr(state), state.shape[1], int(state_off),
+        _ptr(q_start), _ptr(seq_slot), n_seqs, heads, kv_heads, dim, vdim, _stream()), "delta_rule")
+
+
+# -- experts of which a token uses a few ---------------------------------------------------------------------------
+def route_topk(logits: torch.Tensor, top: int, sel_e: torch.Tensor, sel_w: torch.Tensor) -> None:
+    """Per row of the float32 logits [T, E]: the `top` largest (the lower index wins a tie) as indices (int32
+    [T, top]) and their sigmoids as weights (float32 [T, top])."""
+    T, E = logits.shape
+    _need(logits, "router logits", torch.float32)
+    _need(sel_e, "chosen experts", torch.int32, (T, top))
+    _need(sel_w, "experts' weights", torch.float32, (T, top))
+    _check(_lib("routed").jb_route_topk(_ptr(logits), E, E, int(top), _ptr(sel_e), _ptr(sel_w), T, _stream()),
+           "route_topk")
+
+
+def experts_few_tokens(h: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, w_gate: torch.Tensor,
+                       w_up: torch.Tensor, w_down: torch.Tensor, act: torch.Tensor, out: torch.Tensor,
+                       gate_limit: float = 0.0, gate_alpha: float = 1.0) -> None:
+    """out[t] += sum over the token's chosen experts e of Wd_e (act(Wg_e x) * (Wu_e x)) with x = weight * h[t]; the
+    experts' rows are streamed once per (token, expert) pair, sums in float32.  w_gate, w_up [E, F, W], w_down
+    [E, W, F] in h's dtype; act: float32 scratch [T top, F]; out float32 [T, W]."""
+    T, W = h.shape
+    E, F, _ = w_gate.shape
+    top = sel_e.shape[1]
+    _need(h, "expert input")
+    _need(w_gate, "experts' gate", h.dtype, (E, F, W))
+    _need(w_up, "experts' up", h.dtype, (E, F, W))
+    _need(w_down, "experts' down", h.dtype, (E, W, F))
+    _need(sel_e, "chosen experts", torch.int32, (T, top))
+    _need(sel_w, "experts' weights", torch.float32, (T, top))
+    _need(act, "experts' scratch", torch.float32, (T * top, F))
+    _need(out, "experts' out", torch.float32, (T, W))
+    _check(_lib("routed").jb_experts_few_tokens(
+        _ptr(h), dtype_code(h.dtype), _ptr(sel_e), _ptr(sel_w), top, _ptr(w_gate), _ptr(w_up), _ptr(w_down),
+        dtype_code(w_gate.dtype), _ptr(act), _ptr(out), T, W, F, float(gate_limit), float(gate_alpha), _stream()),
+        "experts_few_tokens", kernels=2)
+
+
+def expert_gather(h: torch.Tensor, order: torch.Tensor, sel_w: torch.Tensor, top: int, rows: torch.Tensor) -> None:
+    """rows[i] = weight[order[i]] * h[order[i] // top]: the (token, choice) pairs in the order the experts' products
+    take them."""
+    pairs, W = rows.shape
+    _need(h, "expert input", rows.dtype)
+    _need(rows, "gathered rows")
+    _need(order, "pair order", torch.int32, (pairs,))
+    _need(sel_w, "experts' weights", torch.float32)
+    _check(_lib("routed").jb_expert_gather(_ptr(h), dtype_code(h.dtype), _ptr(order), _ptr(sel_w), int(top), _ptr(rows),
+                                           pairs, W, _stream()), "expert_gather")
+
+
+def expert_scatter(results: torch.Tensor, where: torch.Tensor, top: int, out: torch.Tensor) -> None:
+    """out[t] += sum_k results[where[t * top + k]] (float32)."""
+    T, W = out.shape
+    _need(results, "experts' results", torch.float32)
+    _need(where, "pair places", torch.int32, (T * top,))
+    _need(out, "experts' out", torch.float32)
+    _check(_lib("routed").jb_expert_scatter(_ptr(results), _ptr(where), int(top), _ptr(out), T, W, _stream()),
+           "expert_scatter")

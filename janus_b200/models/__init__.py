@@ -1,1 +1,1 @@
-from . import llama, ramolix, zivitar  # noqa: F401  (registers LlamaForCausalLM, Ramolix and Zivitar)
+from . import llama, mugedra, ramolix, zivitar  # noqa: F401  (registers LlamaForCausalLM, Mugedra, Ramolix and Zivitar)

@@ -136,9 +136,13 @@ class LayerSpec:
 class ScheduleEntry:
     """One place in the order of execution: which layer runs, and whose cache it
     reads (None = its own, written at this place; an earlier place's index = it
-    reads that place's keys and values and writes none)."""
+    reads that place's keys and values and writes none).  `adds_embedding`: right
+    before this place the embedding's output (the residual stream as it was before
+    the first place) is added to the residual stream, as designs do that run a span
+    of layers several times and feed the input in again before every further pass."""
     layer: int
     reads_cache_of: Optional[int] = None
+    adds_embedding: bool = False
 
 
 @dataclass(frozen=True)

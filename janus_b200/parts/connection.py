@@ -61,3 +61,50 @@ class HyperConnection(Connection):
 
 
 register_part("connection", "hyper_connection", HyperConnection)
+
+
+class LayerScale(Connection):
+    """One residual stream; what a sublayer produced is multiplied feature by feature by a weight before it joins:
+    x <- x + scale * y.  The sublayer reads norm(x).  The sum is made in float32; a sublayer's write and the next
+    sublayer's read are one launch where the norm can do both (`join`)."""
+
+    def __init__(self, width: int, dtype: torch.dtype = torch.float32, device: torch.device = torch.device("cuda")):
+        self.width = int(width)
+        self.dtype, self.device = dtype, device
+        self.scale: Optional[torch.Tensor] = None
+
+    def weight_shapes(self):
+        return {"scale": ((self.width,), "ones")}
+
+    def load(self, scale: torch.Tensor) -> None:
+        if tuple(scale.shape) != (self.width,):
+            raise ValueError(f"layer scale of shape {tuple(scale.shape)} does not fit ({self.width},)")
+        self.scale = scale.to(device=self.device, dtype=torch.float32).contiguous()
+
+    def read(self, residual: torch.Tensor, norm, out: torch.Tensor, clear: Optional[torch.Tensor] = None,
+             clear2: Optional[torch.Tensor] = None) -> None:
+        if clear2 is not None and not hasattr(norm, "join"):
+            ops.zero_f32(clear2)
+            clear2 = None
+        if clear is not None and clear.numel() % 4:
+            clear.zero_()
+            clear = None
+        if clear2 is not None:
+            norm.forward(residual, out, clear=clear, clear2=clear2)
+        else:
+            norm.forward(residual, out, clear=clear)
+
+    def write(self, residual: torch.Tensor, y: torch.Tensor) -> None:
+        ops.join_norm(residual, ya=y, scale=self.scale)
+
+    def write_then_read(self, residual: torch.Tensor, y: torch.Tensor, then: "Connection", norm,
+                        out: torch.Tensor, clear2: Optional[torch.Tensor] = None) -> None:
+        """This sublayer's write and the next sublayer's read in one launch; y is left zeroed."""
+        if isinstance(then, LayerScale) and hasattr(norm, "join"):
+            norm.join(residual, y, self.scale, out, clear2=clear2)
+        else:
+            self.write(residual, y)
+            then.read(residual, norm, out, clear=None, clear2=clear2)      # y is zero already
+
+
+register_part("connection", "layer_scale", LayerScale)

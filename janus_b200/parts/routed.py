@@ -1,0 +1,119 @@
+"""A feed-forward made of experts of which every token uses a few.
+
+`experts` gated feed-forwards without biases, expert(x) = Wd (silu(Wg x) * (Wu x)).  The router's logits z = Wr h are
+float32 (the product's own accumulators), the scores s = sigmoid(z); a token's `top` experts are those with the
+largest scores (the lower index wins a tie) and their weights are those scores as they are, not renormalized.  The
+weight multiplies the expert's INPUT: out = sum over the chosen e of expert_e(s_e h).
+
+Steps of few (token, expert) pairs, every single-token step among them, stream each chosen expert's rows once per
+pair (`ops.experts_few_tokens`: two launches, float32 sums, nothing read back by the host, so the step can be
+recorded into a CUDA graph).  Prompt steps of the bfloat16 engine with more pairs read the choice back, gather the
+weighted rows expert by expert and run each expert's two products on the tensor cores over its rows; the results
+are added back token by token in the order of the token's choices.  The float32 engine always streams.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .base import FeedForward, register_part
+from .linear import GatedLinear, Linear
+
+FEW_PAIRS = 64           # up to this many (token, expert) pairs a bfloat16 prompt step streams the experts' rows
+MAX_STREAM_PAIRS = 65535  # pairs of one launch of the streaming kernels
+
+
+class RoutedExperts(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int,
+                 dtype: torch.dtype = torch.bfloat16, device: torch.device = torch.device("cuda")):
+        if not 1 <= top <= experts:
+            raise ValueError(f"a token uses {top} of {experts} experts")
+        if top > 16:
+            raise ValueError(f"at most 16 experts a token are supported, got {top}")
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.experts, self.top = int(experts), int(top)
+        self.dtype, self.device = dtype, device
+        self.router = Linear(hidden_size, experts, dtype, device, name="router", pad_width=True)
+        self.w_gate = self.w_up = self.w_down = None           # [E, F, W], [E, F, W], [E, W, F] row-major
+        self.gate_up: List[GatedLinear] = []                   # bfloat16 engine: the experts' tensor-core products
+        self.down: List[Linear] = []
+
+    def weight_shapes(self):
+        W, F = self.hidden_size, self.intermediate_size
+        shapes = {"router": ((self.experts, W), "normal")}
+        for e in range(self.experts):
+            shapes.update({f"e{e}_gate": ((F, W), "normal"), f"e{e}_up": ((F, W), "normal"),
+                           f"e{e}_down": ((W, F), "normal")})
+        return shapes
+
+    def load(self, router: torch.Tensor, **experts: torch.Tensor) -> None:
+        self.router.load([router])
+        W, F, E = self.hidden_size, self.intermediate_size, self.experts
+
+        def stack(kind: str, shape) -> torch.Tensor:
+            ts = [experts[f"e{e}_{kind}"] for e in range(E)]
+            for t in ts:
+                if tuple(t.shape) != shape:
+                    raise ValueError(f"an expert's '{kind}' of shape {tuple(t.shape)} does not fit {shape}")
+            return torch.stack([t.to(device=self.device, dtype=self.dtype) for t in ts]).contiguous()
+
+        self.w_gate, self.w_up, self.w_down = stack("gate", (F, W)), stack("up", (F, W)), stack("down", (W, F))
+        self.gate_up, self.down = [], []
+        if self.dtype == torch.bfloat16:
+            for e in range(E):
+                gu = GatedLinear(W, F, self.dtype, self.device, name="expert_gate_up", pad_width=True)
+                gu.load(self.w_gate[e], self.w_up[e])
+                dn = Linear(F, W, self.dtype, self.device, name="expert_down", pad_width=True)
+                dn.load([self.w_down[e]])
+                self.gate_up.append(gu)
+                self.down.append(dn)
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+        T = x.shape[0]
+        ws = ctx.workspace
+        logits = ws.get("router_logits", (T, self.experts), torch.float32)
+        self.router.forward(x, logits)
+        sel_e = ws.get("router_experts", (T, self.top), torch.int32)
+        sel_w = ws.get("router_weights", (T, self.top), torch.float32)
+        ops.route_topk(logits, self.top, sel_e, sel_w)
+        pairs = T * self.top
+        if self.dtype == torch.bfloat16 and not ctx.is_decode and pairs > FEW_PAIRS:
+            self._by_expert(x, sel_e, sel_w, residual, ctx)
+            return
+        act = ws.get("experts_act", (pairs, self.intermediate_size), torch.float32)
+        rows = max(1, MAX_STREAM_PAIRS // self.top)
+        for t0 in range(0, T, rows):
+            t1 = min(T, t0 + rows)
+            ops.experts_few_tokens(x[t0:t1], sel_e[t0:t1], sel_w[t0:t1], self.w_gate, self.w_up, self.w_down,
+                                   act[t0 * self.top: t1 * self.top], residual[t0:t1])
+
+    def _by_expert(self, x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+        """The tensor-core path of a prompt step: the host reads the choice, sorts the (token, choice) pairs by expert
+        and launches each expert's products over its rows."""
+        T, W, F, top = x.shape[0], self.hidden_size, self.intermediate_size, self.top
+        pairs = T * top
+        chosen = sel_e.reshape(-1).cpu().numpy()                  # waits for the router
+        order = np.argsort(chosen, kind="stable").astype(np.int32)
+        where = np.empty(pairs, dtype=np.int32)
+        where[order] = np.arange(pairs, dtype=np.int32)
+        counts = np.bincount(chosen, minlength=self.experts)
+        index = torch.from_numpy(np.concatenate([order, where])).to(self.device)
+        ws = ctx.workspace
+        rows = ws.get("experts_rows", (pairs, W), self.dtype)
+        ops.expert_gather(x, index[:pairs], sel_w, top, rows)
+        act = ws.get("experts_act_rows", (pairs, F), self.dtype)
+        results = ws.get("experts_results", (pairs, W), torch.float32)
+        start = 0
+        for e in range(self.experts):
+            n = int(counts[e])
+            if n:
+                self.gate_up[e].forward(rows[start:start + n], act[start:start + n], ctx)
+                self.down[e].forward(act[start:start + n], results[start:start + n])
+                start += n
+        ops.expert_scatter(results, index[pairs:], top, residual)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)
