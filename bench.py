@@ -21,7 +21,7 @@ the same weights (`checked`).
 
 Other modes (one JSON line per item, none of them the headline): --kernels,
 --prompt-lengths, --workload 1b|13b, --deterministic, --plan-check, --cpu-baseline, --float32, --design
-(the Zivitar design, or with --design-model ramolix the Ramolix design, beside the Llama decoder at equal layer
+(the Zivitar design, or with --design-model ramolix | mugedra another one, beside the Llama decoder at equal layer
 sizes: prompt and decode throughput, a step's kernels).
 """
 import argparse
@@ -686,11 +686,30 @@ def llama_like(width, ff, heads, kv_heads, window, vocab):
                 tie_word_embeddings=False)
 
 
-DESIGNS = {"zivitar": zivitar_config, "ramolix": ramolix_config}
+def mugedra_config(width, ff, heads, kv_heads, window, vocab):
+    """Three layers at the size's width of which the middle one runs twice (four layer runs): capped attention in
+    chunks of the size's window (head size 128, half of it rotated) beside a gated delta rule (as many heads of 128
+    by 128 state, four taps), and eight experts of half the size's feed-forward each of which a token uses two (the
+    dense feed-forward's products per token)."""
+    layer = dict(type="parallel",
+                 mixer=dict(left=dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, softcap=50.0,
+                                      mask=dict(size=window),
+                                      rot=dict(dims=64, base=10000.0, scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0))),
+                            right=dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, conv=4)),
+                 mlp=dict(kind="moe", expert=dict(ff=ff // 2), router=dict(experts=8, top=2)))
+    return dict(architecture="Mugedra", vocab=vocab, width=width, norm=dict(eps=1e-5), loop=dict(start=1, stop=2, times=2),
+                layers=[layer, layer, layer])
+
+
+DESIGNS = {"zivitar": zivitar_config, "ramolix": ramolix_config, "mugedra": mugedra_config}
+# what a design is measured beside: the Llama decoder, or the design whose kernels are most like its own
+BESIDE = {"zivitar": ("llama",), "ramolix": ("llama",), "mugedra": ("ramolix", "llama")}
 
 
 def run_design(which, design="zivitar"):
-    """A design (Zivitar or Ramolix) beside the Llama decoder at equal layer sizes (random weights, four layers):
+    """A design (Zivitar, Ramolix or Mugedra) beside the Llama decoder, and Mugedra also beside Ramolix, whose
+    mixers (a recurrence behind a short convolution, attention over part of the keys) are most like its own, at equal
+    layer sizes (random weights, four layer runs):
     prompt steps and decode steps timed on the device, and each step's kernels one by one (`Model.profile`).  One
     JSON line per (size, model)."""
     import torch
@@ -699,7 +718,8 @@ def run_design(which, design="zivitar"):
     from janus_b200.engine.step import StepEntry
     for name in which.split(","):
         size = DESIGN_SIZES[name]
-        for label, cfg in ((design, DESIGNS[design](**size)), ("llama", llama_like(**size))):
+        for label in (design,) + BESIDE[design]:
+            cfg = llama_like(**size) if label == "llama" else DESIGNS[label](**size)
             model = janus_b200.load_random(cfg, seed=5, dtype="bfloat16", max_tokens=8 * 2176 + 8192 + 1024, max_slots=16,
                                            max_seq_len=16384, norm_std=0.0)
             V = size["vocab"]

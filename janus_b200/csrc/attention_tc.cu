@@ -269,12 +269,32 @@ __device__ __forceinline__ void scale16(uint32_t* r, float f) {
   }
 }
 
+// A chunked mask and capped scores.  chunk > 0: a query sees only the keys of its own chunk of positions,
+// [floor(pos / chunk) chunk, pos].  cap_s > 0: a raw score s becomes cap_s tanh(s inv_cap), with cap_s = cap / scale
+// and inv_cap = scale / cap, so that the scale applied afterwards gives cap tanh(s scale / cap).
+struct Cap {
+  int chunk;
+  float cap_s, inv_cap;
+};
+__device__ __forceinline__ int chunk_lo(int lo, int pos, int chunk) {
+  return (chunk > 0 && pos >= 0) ? max(lo, (pos / chunk) * chunk) : lo;
+}
+// tanh(x) = 1 - 2 / (1 + e^2x): absolute error of a few 1e-7, which is what a score needs
+__device__ __forceinline__ float tanh_abs(float x) {
+  return 1.0f - __fdividef(2.0f, 1.0f + fast_exp2(x * 2.8853900817779268f));
+}
+template <int N>
+__device__ __forceinline__ void cap_scores(uint32_t* sr, const Cap& cap) {
+#pragma unroll
+  for (int c = 0; c < N; ++c) sr[c] = __float_as_uint(cap.cap_s * tanh_abs(__uint_as_float(sr[c]) * cap.inv_cap));
+}
+
 template <int NT>
 __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
     const int* __restrict__ q_start, const int* __restrict__ kv_len, int nh, int nkv, int hd, int max_pages, int window,
-    float scale_log2, int heads_slowest, int* __restrict__ status) {
+    float scale_log2, int heads_slowest, int* __restrict__ status, Cap cap) {
   // S of tile w: two buffers of 64 columns at w * 128; O behind them (HD columns a tile; 512 in all for rows of 256)
   constexpr int N_BARS = bars_for(NT), TMEM_COLS = HD > 128 ? 512 : NT * 256, TMEM_S0 = 0, TMEM_O0 = NT * 128;
   static_assert(NT * 128 + NT * HD <= TMEM_COLS, "tensor memory of one CTA");
@@ -342,7 +362,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
   // both tiles walk the same pages, from the first page any of their rows sees to the last; rows mask what is
   // not theirs (the first tile's rows see nothing of the last page or two)
   const int kb_end = active ? (pos_first + n_tok_all - 1) / PAGE : -1;
-  const int kb_start = (active && window > 0) ? max(0, pos_first - window + 1) / PAGE : 0;
+  const int kb_start = active ? chunk_lo(window > 0 ? max(0, pos_first - window + 1) : 0, pos_first, cap.chunk) / PAGE : 0;
   const int nb = kb_end - kb_start + 1;
 
   if (active && warp == 0) {
@@ -418,7 +438,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
     const int tl = w * tpt + row / G;          // token within the pair
     const bool valid = row < tpt * G && tl < n_tok_all;   // rows past tpt * G belong to no token
     const int row_pos = valid ? pos_first + tl : -1;
-    const int row_lo = window > 0 ? max(0, row_pos - window + 1) : 0;
+    const int row_lo = chunk_lo(window > 0 ? max(0, row_pos - window + 1) : 0, row_pos, cap.chunk);
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     const uint32_t s_col = TMEM_S0 + w * 128, o_col = TMEM_O0 + w * HD;
     float m_ref = -CUDART_INF_F, l = 0.0f;   // l is the row sum relative to m_ref
@@ -432,6 +452,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
 #pragma unroll
       for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(lane_addr + s_col + b * 64 + c0, sr + c0);
       tmem_ld_wait();
+      if (cap.cap_s > 0.0f) cap_scores<64>(sr, cap);
       const int key0 = (kb_start + j) * PAGE;
       if (key0 + PAGE - 1 > row_pos || key0 < row_lo) {   // only blocks that touch the causal edge or the window
 #pragma unroll
@@ -529,7 +550,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
     const int* __restrict__ q_start, const int* __restrict__ kv_len, int nh, int nkv, int hd, int max_pages, int window,
-    float scale_log2, int heads_slowest, int* __restrict__ status) {
+    float scale_log2, int heads_slowest, int* __restrict__ status, Cap cap) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t q_s = smem_u32(smem);
@@ -587,7 +608,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
   const int pos_first = len - q_len + tok_first;
   const int last_page = (len - 1) / PAGE;
   const int kb_end = active ? (pos_first + n_tok_all - 1) / KB : -1;                       // in blocks of 128 keys
-  const int kb_start = (active && window > 0) ? max(0, pos_first - window + 1) / KB : 0;
+  const int kb_start = active ? chunk_lo(window > 0 ? max(0, pos_first - window + 1) : 0, pos_first, cap.chunk) / KB : 0;
   const int nb = kb_end - kb_start + 1;
 
   if (active && warp == 0) {
@@ -667,7 +688,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
     const int tl = w * tpt + row / G;
     const bool valid = row < tpt * G && tl < n_tok_all;   // rows past tpt * G belong to no token
     const int row_pos = valid ? pos_first + tl : -1;
-    const int row_lo = window > 0 ? max(0, row_pos - window + 1) : 0;
+    const int row_lo = chunk_lo(window > 0 ? max(0, row_pos - window + 1) : 0, row_pos, cap.chunk);
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     const uint32_t s_col = w * 128, o_col = 256 + w * 128;
     float m_ref = -CUDART_INF_F, l = 0.0f;
@@ -680,6 +701,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
 #pragma unroll
       for (int c0 = 0; c0 < KB; c0 += 16) tmem_ld16(lane_addr + s_col + c0, sr + c0);
       tmem_ld_wait();
+      if (cap.cap_s > 0.0f) cap_scores<KB>(sr, cap);
       const int key0 = (kb_start + j) * KB;
       if (key0 + KB - 1 > row_pos || key0 < row_lo) {
 #pragma unroll
@@ -778,11 +800,11 @@ JB_EXPORT int jb_attention_tc_head_dim() { return HD; }
 
 // q, out: [T, nh * hd] bf16; caches: [n_pages, nkv, 64, hd] bf16.  Needs nh / nkv <= 128 and a head size
 // that is a multiple of 8 (rows of 16 bytes for the tensor maps) up to the build's row.
-JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                      const int* block_table, const int* q_start, const int* kv_len, int T,
-                                      int n_pages, int n_seqs, int max_q_len, int nh, int nkv, int hd,
-                                      int page_size, int max_pages, int window, float scale, int* status,
-                                      cudaStream_t stream) {
+namespace {
+int tc_prefill_launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                      const int* q_start, const int* kv_len, int T, int n_pages, int n_seqs, int max_q_len, int nh,
+                      int nkv, int hd, int page_size, int max_pages, int window, float scale, const Cap& cap,
+                      int* status, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0 || T <= 0) return 0;
   JB_REFUSE(hd <= 0 || hd > HD || hd % 8 != 0,
             "attention_tc: built for head sizes up to %d in steps of 8, called with %d", HD, hd);
@@ -846,11 +868,34 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
     dim3 grid(heads_slowest ? n_pairs : nkv, heads_slowest ? nkv : n_pairs, n_seqs);
     jb::Launch cfg(grid, dim3(T2_THREADS), T2_SMEM, stream);
     return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc128_kernel, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
-                                   nkv, hd, max_pages, window, scale * LOG2E, heads_slowest ? 1 : 0, status);
+                                   nkv, hd, max_pages, window, scale * LOG2E, heads_slowest ? 1 : 0, status, cap);
   }
 #endif
   dim3 grid(heads_slowest ? n_tiles : nkv, heads_slowest ? nkv : n_tiles, n_seqs);
   jb::Launch cfg(grid, dim3(threads_for(1)), smem_for(1), stream);
   return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc_kernel<1>, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
-                                 nkv, hd, max_pages, window, scale * LOG2E, heads_slowest ? 1 : 0, status);
+                                 nkv, hd, max_pages, window, scale * LOG2E, heads_slowest ? 1 : 0, status, cap);
+}
+}  // namespace
+
+JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                      const int* block_table, const int* q_start, const int* kv_len, int T,
+                                      int n_pages, int n_seqs, int max_q_len, int nh, int nkv, int hd,
+                                      int page_size, int max_pages, int window, float scale, int* status,
+                                      cudaStream_t stream) {
+  return tc_prefill_launch(q, k_cache, v_cache, out, block_table, q_start, kv_len, T, n_pages, n_seqs, max_q_len, nh,
+                           nkv, hd, page_size, max_pages, window, scale, Cap{0, 0.0f, 0.0f}, status, stream);
+}
+
+// As jb_attention_tc_prefill, with a chunked mask (chunk > 0: a query sees only the keys of its own chunk of
+// positions, counted from the sequence's first) and capped scores (softcap > 0: s -> softcap tanh(s / softcap)).
+JB_EXPORT int jb_attention_tc_prefill_capped(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                             const int* block_table, const int* q_start, const int* kv_len, int T,
+                                             int n_pages, int n_seqs, int max_q_len, int nh, int nkv, int hd,
+                                             int page_size, int max_pages, int window, float scale, int chunk,
+                                             float softcap, int* status, cudaStream_t stream) {
+  JB_REFUSE(chunk < 0 || softcap < 0.0f || scale <= 0.0f, "attention_tc: a chunk, a cap and a scale cannot be negative");
+  const Cap cap = softcap > 0.0f ? Cap{chunk, softcap / scale, scale / softcap} : Cap{chunk, 0.0f, 0.0f};
+  return tc_prefill_launch(q, k_cache, v_cache, out, block_table, q_start, kv_len, T, n_pages, n_seqs, max_q_len, nh,
+                           nkv, hd, page_size, max_pages, window, scale, cap, status, stream);
 }

@@ -27,7 +27,32 @@ __device__ __forceinline__ void clear_slice(float4* buf, size_t n4) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) buf[i] = z;
 }
 
-template <typename TO>
+// V floats at a time (4: rows of whole, aligned 16-byte vectors; 1: any row)
+template <int V> struct Vec;
+template <> struct Vec<1> {
+  float v[1];
+  __device__ __forceinline__ void load(const float* p) { v[0] = *p; }
+  __device__ __forceinline__ void store(float* p) const { *p = v[0]; }
+};
+template <> struct Vec<4> {
+  float v[4];
+  __device__ __forceinline__ void load(const float* p) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+  }
+  __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <int V> __device__ __forceinline__ void store_out(float* p, const Vec<V>& x) { x.store(p); }
+__device__ __forceinline__ void store_out(bf16* p, const Vec<1>& x) { *p = __float2bfloat16(x.v[0]); }
+__device__ __forceinline__ void store_out(bf16* p, const Vec<4>& x) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(x.v[0], x.v[1]), hi = __floats2bfloat162_rn(x.v[2], x.v[3]);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&lo);
+  u.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TO, int V>
 __global__ void join_norm_kernel(float* __restrict__ stream, float* __restrict__ ya, float* __restrict__ yb,
                                  const float* __restrict__ wa, const float* __restrict__ wb, float mult,
                                  const float* __restrict__ scale, const float* __restrict__ extra,
@@ -42,48 +67,93 @@ __global__ void join_norm_kernel(float* __restrict__ stream, float* __restrict__
   clear_slice(clear2, clear2_n4);
   const size_t src = row_index != nullptr ? (size_t)row_index[blockIdx.x] : (size_t)blockIdx.x;
   float* r = stream + src * W;
+  float* pa = ya != nullptr ? ya + src * W : nullptr;
+  float* pb = yb != nullptr ? yb + src * W : nullptr;
+  const int first = threadIdx.x * V, step = blockDim.x * V;
+  const bool branches = pa != nullptr && wa != nullptr;
   float inv_a = 1.0f, inv_b = 1.0f;
-  if (ya != nullptr && wa != nullptr) {
+  if (branches) {
     float sa = 0.0f, sb = 0.0f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-      const float a = ya[src * W + i], b = yb[src * W + i];
-      sa = fmaf(a, a, sa);
-      sb = fmaf(b, b, sb);
+    for (int i = first; i < W; i += step) {
+      Vec<V> a, b;
+      a.load(pa + i);
+      b.load(pb + i);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        sa = fmaf(a.v[j], a.v[j], sa);
+        sb = fmaf(b.v[j], b.v[j], sb);
+      }
     }
     sa = jb::block_sum(sa, scratch);
     sb = jb::block_sum(sb, scratch);
     inv_a = 1.0f / sqrtf(sa / (float)W + eps);
     inv_b = 1.0f / sqrtf(sb / (float)W + eps);
   }
+  Vec<V> zero;
+#pragma unroll
+  for (int j = 0; j < V; ++j) zero.v[j] = 0.0f;
   float sum = 0.0f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    float v = r[i];
-    if (ya != nullptr) {
-      float y = ya[src * W + i];
-      ya[src * W + i] = 0.0f;
-      if (wa != nullptr) {
-        y = mult * ((y * inv_a) * wa[i] + (yb[src * W + i] * inv_b) * wb[i]);
-        yb[src * W + i] = 0.0f;
+  for (int i = first; i < W; i += step) {
+    Vec<V> v;
+    v.load(r + i);
+    if (pa != nullptr) {
+      Vec<V> y;
+      y.load(pa + i);
+      zero.store(pa + i);
+      if (branches) {
+        Vec<V> b, ga, gb;
+        b.load(pb + i);
+        zero.store(pb + i);
+        ga.load(wa + i);
+        gb.load(wb + i);
+#pragma unroll
+        for (int j = 0; j < V; ++j) y.v[j] = mult * ((y.v[j] * inv_a) * ga.v[j] + (b.v[j] * inv_b) * gb.v[j]);
       }
-      v = scale != nullptr ? fmaf(scale[i], y, v) : v + y;
+      if (scale != nullptr) {
+        Vec<V> sc;
+        sc.load(scale + i);
+#pragma unroll
+        for (int j = 0; j < V; ++j) v.v[j] = fmaf(sc.v[j], y.v[j], v.v[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) v.v[j] += y.v[j];
+      }
     }
-    if (extra != nullptr) v += extra[src * W + i];
-    if (ya != nullptr || extra != nullptr) r[i] = v;
-    row_s[i] = v;
-    sum += v;
+    if (extra != nullptr) {
+      Vec<V> x;
+      x.load(extra + src * W + i);
+#pragma unroll
+      for (int j = 0; j < V; ++j) v.v[j] += x.v[j];
+    }
+    if (pa != nullptr || extra != nullptr) v.store(r + i);
+    v.store(row_s + i);
+#pragma unroll
+    for (int j = 0; j < V; ++j) sum += v.v[j];
   }
   if (x_out == nullptr) return;
   float mean = 0.0f;
   if (center) mean = jb::block_sum(sum, scratch) / (float)W;
   float sq = 0.0f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {   // a thread reads back what it wrote itself
-    const float d = row_s[i] - mean;
-    sq = fmaf(d, d, sq);
+  for (int i = first; i < W; i += step) {   // a thread reads back what it wrote itself
+    Vec<V> v;
+    v.load(row_s + i);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float d = v.v[j] - mean;
+      sq = fmaf(d, d, sq);
+    }
   }
   sq = jb::block_sum(sq, scratch);
   const float inv = 1.0f / sqrtf(sq / (float)W + eps);
   TO* x = x_out + (size_t)blockIdx.x * W;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) x[i] = jb::from_f32<TO>(((row_s[i] - mean) * inv) * gamma[i]);
+  for (int i = first; i < W; i += step) {
+    Vec<V> v, g;
+    v.load(row_s + i);
+    g.load(gamma + i);
+#pragma unroll
+    for (int j = 0; j < V; ++j) v.v[j] = ((v.v[j] - mean) * inv) * g.v[j];
+    store_out(x + i, v);
+  }
 }
 
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * act(gate[t, h, :]), one warp per (token, head);
@@ -147,20 +217,27 @@ JB_EXPORT int jb_join_norm(float* stream, float* ya, float* yb, const float* wa,
   JB_REFUSE(x_out != nullptr && gamma == nullptr, "join_norm: a norm needs its weight");
   const size_t smem = (size_t)W * sizeof(float);
   JB_REFUSE(smem > 200 * 1024, "join_norm: a row of %d floats does not fit shared memory", W);
-  jb::Launch cfg(dim3(T), dim3(W >= 2048 ? 512 : W >= 512 ? 256 : 128), smem, stream_);
+  // rows of whole 16-byte vectors at aligned addresses are read and written four floats at a time
+  const uintptr_t all = (uintptr_t)stream | (uintptr_t)ya | (uintptr_t)yb | (uintptr_t)wa | (uintptr_t)wb |
+                        (uintptr_t)scale | (uintptr_t)extra | (uintptr_t)gamma | (uintptr_t)x_out;
+  const bool vec = W % 4 == 0 && (all & 15) == 0;
+  const int per = vec ? 4 : 1;
+  jb::Launch cfg(dim3(T), dim3(W >= 2048 * per ? 512 : W >= 512 * per ? 256 : 128), smem, stream_);
   cudaError_t e;
-#define JB_LAUNCH_JN(TO)                                                                                           \
+#define JB_LAUNCH_JN(TO, V)                                                                                        \
   do {                                                                                                             \
     if (smem > 48 * 1024) {                                                                                        \
-      e = cudaFuncSetAttribute(join_norm_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+      e = cudaFuncSetAttribute(join_norm_kernel<TO, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
       if (e != cudaSuccess) return (int)e;                                                                         \
     }                                                                                                              \
-    e = cudaLaunchKernelEx(&cfg.c, join_norm_kernel<TO>, stream, ya, yb, wa, wb, mult, scale, extra, gamma, eps,   \
+    e = cudaLaunchKernelEx(&cfg.c, join_norm_kernel<TO, V>, stream, ya, yb, wa, wb, mult, scale, extra, gamma, eps, \
                            center, (TO*)x_out, row_index, W, (float4*)clear, clear ? (size_t)clear_n >> 2 : (size_t)0, \
                            (float4*)clear2, clear2 ? (size_t)clear2_n >> 2 : (size_t)0);                           \
   } while (0)
-  if (out_dtype == JB_F32) JB_LAUNCH_JN(float);
-  else if (out_dtype == JB_BF16) JB_LAUNCH_JN(bf16);
+  if (out_dtype == JB_F32 && vec) JB_LAUNCH_JN(float, 4);
+  else if (out_dtype == JB_F32) JB_LAUNCH_JN(float, 1);
+  else if (out_dtype == JB_BF16 && vec) JB_LAUNCH_JN(bf16, 4);
+  else if (out_dtype == JB_BF16) JB_LAUNCH_JN(bf16, 1);
   else return JB_ERR_BAD_DTYPE;
 #undef JB_LAUNCH_JN
   return (int)e;

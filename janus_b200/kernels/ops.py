@@ -68,7 +68,7 @@ _SIGNATURES = {
     "jb_delta_rule": "piiiipiiippfppllppiiiiip",
     "jb_route_topk": "piiippip", "jb_experts_few_tokens": "pippipppippiiiffp", "jb_expert_gather": "pippipiip",
     "jb_expert_scatter": "ppipiip",
-    "jb_attention_tc_prefill": "pppppppiiiiiiiiiifpp",
+    "jb_attention_tc_prefill": "pppppppiiiiiiiiiifpp", "jb_attention_tc_prefill_capped": "pppppppiiiiiiiiiififpp",
     "jb_streams_rmsnorm": "pppipifpiiipplp", "jb_streams_mix": "ppppiiip", "jb_streams_mix_rmsnorm": "pppppipifpiiiplp", "jb_embed_streams": "pippiiippp",
     "jb_lightning_scan": "piiiipppppiiiiiipp", "jb_gated_rmsnorm": "ppipifpiiip",
     "jb_conv_rope_cache": "pipipipppppippppiiiiiiip", "jb_conv_state_update": "pipippiip",
@@ -905,8 +905,8 @@ def _attention_tc_row(hd: int) -> int:
 def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                          block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor,
                          n_seqs: int, max_q_len: int, nh: int, nkv: int, hd: int, page_size: int,
-                         window: int, scale: float) -> None:
-    """As attention_bf16_prefill, on the tcgen05 tensor cores."""
+                         window: int, scale: float, chunk: int = 0, softcap: float = 0.0) -> None:
+    """As attention_bf16_prefill, on the tcgen05 tensor cores.  `chunk`, `softcap`: as in `attention_f32`."""
     T = q.shape[0]
     _need(q, "attention q", torch.bfloat16, (T, nh * hd))
     _need(out, "attention out", torch.bfloat16, (T, nh * hd))
@@ -917,8 +917,14 @@ def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     _need(kv_len, "kv_len", torch.int32, (n_seqs,))
     if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or k_cache.shape != v_cache.shape:
         raise KernelError(f"attention_tc: cache shape {tuple(k_cache.shape)} does not fit [pages, {nkv}, {page_size}, {hd}]")
-    _check(_lib("attention_tc", _attention_tc_row(hd),
-                lambda h: dict({"JB_HEAD_DIM": h}, **_ATTN_TC_DEFINES)).jb_attention_tc_prefill(
+    lib = _lib("attention_tc", _attention_tc_row(hd), lambda h: dict({"JB_HEAD_DIM": h}, **_ATTN_TC_DEFINES))
+    if chunk or softcap:
+        _check(lib.jb_attention_tc_prefill_capped(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
+            T, k_cache.shape[0], n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window),
+            scale, int(chunk), float(softcap), _ptr(kernel_status(q.device)), _stream()), "attention_tc_prefill")
+        return
+    _check(lib.jb_attention_tc_prefill(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
         T, k_cache.shape[0], n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window),
         scale, _ptr(kernel_status(q.device)), _stream()), "attention_tc_prefill")

@@ -9,8 +9,8 @@ floor(i / chunk) = floor(j / chunk), chunks counted from the sequence's first po
 ordinary softmax.  The concatenated heads are multiplied by sigmoid(Wg h) and projected by Wo.
 
 q, k, v and the gate are one stacked product whose float32 accumulators one kernel turns into the queries and the
-cache rows (`ops.head_norm_rope_cache`); the attention itself is the library's grouped-query attention with the cap
-and the chunk as arguments.  Keys and values share one stored head size, the larger of dim and vdim (the extra
+cache rows (`ops.head_norm_rope_cache`); the attention itself is the library's grouped-query attention (tcgen05 for
+prompts, split keys for single tokens) with the cap and the chunk as arguments.  Keys and values share one stored head size, the larger of dim and vdim (the extra
 columns are zero: scores and sums do not change).
 """
 from __future__ import annotations
@@ -118,6 +118,10 @@ class CappedAttention(Mixer):
                                       self.nkv, D, group.page_size, 0, self.scale, ctx.workspace,
                                       min(ctx.max_kv_len_bound, self.chunk) if self.chunk else ctx.max_kv_len_bound,
                                       chunk=self.chunk, softcap=self.softcap)
+        elif ops.attention_tc_supported(self.nh, self.nkv, D):
+            ops.attention_tc_prefill(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.q_start, ctx.kv_len,
+                                     ctx.n_seqs, ctx.max_q_len, self.nh, self.nkv, D, group.page_size, 0, self.scale,
+                                     self.chunk, self.softcap)
         else:
             ops.attention_bf16_prefill(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.q_start, ctx.kv_len,
                                        ctx.n_seqs, ctx.max_q_len, self.nh, self.nkv, D, group.page_size, 0, self.scale,

@@ -423,6 +423,59 @@ def test_router_and_expert_kernels_against_the_plain_feed_forward():
         assert rel_err(acc.cpu(), want_acc) < 1e-6
 
 
+@gpu
+@pytest.mark.parametrize("tiles", ["1", "2"])
+@pytest.mark.parametrize("nh,nkv,hd,chunk,cap", [(8, 2, 64, 130, 5.0), (4, 4, 128, 64, 0.0), (6, 2, 32, 0, 2.0),
+                                                 (8, 1, 128, 200, 50.0)])
+def test_prompt_attention_kernels_with_chunks_and_a_cap_against_the_plain_softmax(monkeypatch, tiles, nh, nkv, hd, chunk, cap):
+    """The tensor-core prompt kernel (one row tile a block, and two), the mma.sync one and the float32 one on the same
+    pages: a prompt from position 0 and a portion that starts at position 300 of a longer sequence, pages out of order."""
+    from janus_b200.kernels import ops
+    if not ops.attention_tc_supported(nh, nkv, hd):
+        pytest.skip("the tensor-core kernel does not take this shape")
+    monkeypatch.setenv("JANUS_ATTN_TC_TILES", tiles)
+    g = torch.Generator().manual_seed(hd + chunk)
+    scale = 2.0 * hd ** -0.5
+    lens, starts = (333, 500), (0, 300)
+    n_pages = sum((n + 63) // 64 for n in lens) + 3
+    order = torch.randperm(n_pages, generator=g).tolist()
+    kc = torch.zeros(n_pages, nkv, 64, hd, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    table = torch.zeros(2, 8, dtype=torch.int32)
+    qs, want = [], []
+    for i, (n, start) in enumerate(zip(lens, starts)):
+        k = torch.randn(n, nkv, hd, generator=g).to(torch.bfloat16)
+        v = torch.randn(n, nkv, hd, generator=g).to(torch.bfloat16)
+        q = torch.randn(n - start, nh, hd, generator=g).to(torch.bfloat16)
+        for pg in range((n + 63) // 64):
+            page = order.pop()
+            table[i, pg] = page
+            rows = slice(pg * 64, min(n, pg * 64 + 64))
+            kc[page, :, : rows.stop - rows.start] = k[rows].transpose(0, 1)
+            vc[page, :, : rows.stop - rows.start] = v[rows].transpose(0, 1)
+        qs.append(q)
+        want.append(P.chunk_softmax(q.to(P.DT), k.to(P.DT), v.to(P.DT), start, scale, cap or None, chunk or None))
+    q = torch.cat(qs).reshape(-1, nh * hd).cuda()
+    want = torch.cat(want).reshape(-1, nh * hd)
+    q_start = torch.tensor([0, lens[0] - starts[0], lens[0] - starts[0] + lens[1] - starts[1]], dtype=torch.int32).cuda()
+    kv_len = torch.tensor(lens, dtype=torch.int32).cuda()
+    out = torch.zeros_like(q)
+    args = (q, kc.cuda(), vc.cuda(), out, table.cuda(), q_start, kv_len, 2, lens[0], nh, nkv, hd, 64, 0, scale, chunk, cap)
+    ops.attention_tc_prefill(*args)
+    assert rel_err(out.float().cpu(), want) < 1e-2
+    out.zero_()
+    ops.attention_bf16_prefill(*args)
+    assert rel_err(out.float().cpu(), want) < 1e-2
+    if tiles == "1":
+        token_seq = torch.tensor([0] * (lens[0] - starts[0]) + [1] * (lens[1] - starts[1]), dtype=torch.int32).cuda()
+        positions = torch.cat([torch.arange(starts[i], lens[i], dtype=torch.int32) for i in range(2)]).cuda()
+        out32 = torch.zeros(q.shape, device="cuda")
+        ops.attention_f32(q.float(), kc.float().cuda(), vc.float().cuda(), out32, table.cuda(), token_seq, positions, nh, nkv,
+                          hd, 64, 0, scale, chunk, cap)
+        assert rel_err(out32.cpu(), want) < 1e-5
+    ops.check_kernel_status(q.device)
+
+
 def _one_branch(cfg, w, side):
     """The same model with the other branch silenced: its output projection is zero, so its normed output is too."""
     out = dict(w)
