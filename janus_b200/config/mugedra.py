@@ -127,8 +127,8 @@ def _read_left(raw: Dict[str, Any], where: str) -> ChunkAttentionConfig:
     heads, kv_heads = _heads(r, where)
     dim = r.integer("dim")
     chunk = 0
-    if raw.get("mask") is not None:
-        chunk = KeyReader(_object(raw["mask"], where + ".mask")).integer("size")
+    if raw.get("mask") is not None and _object(raw["mask"], where + ".mask").get("size") is not None:
+        chunk = KeyReader(raw["mask"]).integer("size")
     rot = None
     if raw.get("rot") is not None:
         rr = _object(raw["rot"], where + ".rot")
