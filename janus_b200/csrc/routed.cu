@@ -1,5 +1,5 @@
 // A feed-forward made of experts of which every token uses a few: the router's choice, the experts' products for
-// steps of few tokens (every chosen expert's rows are streamed once per token that chose it, float32 sums), and the
+// steps of few tokens (every chosen expert's rows are streamed once for up to four tokens that chose it, float32 sums), and the
 // bookkeeping around the tensor-core products of steps with many tokens (rows gathered expert by expert, results
 // added back token by token).
 //
@@ -79,113 +79,184 @@ template <> struct Vec<bf16> {
 
 constexpr int GU_WARPS = 8, GU_ROWS = 2;   // rows of gate (and of up) per warp
 
-// act[pair][f] = gated(Wg_e[f] . x, Wu_e[f] . x) with x = weight[pair] * h[token of the pair]
-template <typename TW, typename TX, bool VEC>
+// The pairs among [base, base + blockDim.x) that chose expert e, in list[0 .. n) (in no fixed order: every pair's
+// result is computed by itself, so the order changes nothing).
+__device__ __forceinline__ int pairs_of_expert(const int* __restrict__ sel_e, int n_pairs, int base, int e, int* list,
+                                               int* count) {
+  if (threadIdx.x == 0) *count = 0;
+  __syncthreads();
+  const int pr = base + threadIdx.x;
+  if (pr < n_pairs && sel_e[pr] == e) list[atomicAdd(count, 1)] = pr;
+  __syncthreads();
+  return *count;
+}
+
+// act[pair][f] = gated(Wg_e[f] . x, Wu_e[f] . x) with x = weight[pair] * h[token of the pair].  A block owns rows of
+// ONE expert (blockIdx.y) and serves every pair that chose it, PB pairs at a time: the expert's rows come from
+// memory once however many of the step's tokens chose it, and not at all when none did.
+template <typename TW, typename TX, bool VEC, int PB>
 __global__ void __launch_bounds__(GU_WARPS * 32) expert_gate_up_kernel(
-    const TX* __restrict__ h, const int* __restrict__ sel_e, const float* __restrict__ sel_w, int top,
+    const TX* __restrict__ h, const int* __restrict__ sel_e, const float* __restrict__ sel_w, int top, int n_pairs,
     const TW* __restrict__ w_gate, const TW* __restrict__ w_up, float* __restrict__ act, int W, int F, jb::Gate gate) {
-  extern __shared__ __align__(16) float x_s[];
+  extern __shared__ __align__(16) float x_s[];           // [PB][W]
+  __shared__ int list[GU_WARPS * 32];
+  __shared__ int count;
   jb::pdl_launch_dependents();
   jb::pdl_wait();
-  const int pair = blockIdx.y, t = pair / top;
-  const int e = sel_e[pair];
-  const float s = sel_w[pair];
-  for (int i = threadIdx.x; i < W; i += blockDim.x) x_s[i] = s * jb::to_f32(h[(size_t)t * W + i]);
-  __syncthreads();
+  const int e = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = (blockIdx.x * GU_WARPS + warp) * GU_ROWS;
-  if (f0 >= F) return;
-  const TW* g_rows = w_gate + ((size_t)e * F + f0) * W;
-  const TW* u_rows = w_up + ((size_t)e * F + f0) * W;
-  float ag[GU_ROWS], au[GU_ROWS];
-#pragma unroll
-  for (int r = 0; r < GU_ROWS; ++r) ag[r] = au[r] = 0.0f;
-  if (VEC) {
-    constexpr int N = Vec<TW>::N;
-    for (int i = lane * N; i < W; i += 32 * N) {
-      float gv[GU_ROWS][N], uv[GU_ROWS][N];
-#pragma unroll
-      for (int r = 0; r < GU_ROWS; ++r) {
-        const size_t off = (size_t)(f0 + r < F ? r : 0) * W + i;
-        Vec<TW>::load(g_rows + off, gv[r]);
-        Vec<TW>::load(u_rows + off, uv[r]);
+  const TW* g_rows = w_gate + ((size_t)e * F + min(f0, F - 1)) * W;
+  const TW* u_rows = w_up + ((size_t)e * F + min(f0, F - 1)) * W;
+  for (int base = 0; base < n_pairs; base += blockDim.x) {
+    const int n = pairs_of_expert(sel_e, n_pairs, base, e, list, &count);
+    for (int g0 = 0; g0 < n; g0 += PB) {
+      const int nb = min(PB, n - g0);
+      for (int b = 0; b < nb; ++b) {
+        const int pair = list[g0 + b];
+        const float s = sel_w[pair];
+        const TX* src = h + (size_t)(pair / top) * W;
+        for (int i = threadIdx.x; i < W; i += blockDim.x) x_s[(size_t)b * W + i] = s * jb::to_f32(src[i]);
       }
+      __syncthreads();
+      if (f0 < F) {
+        float ag[GU_ROWS][PB], au[GU_ROWS][PB];
 #pragma unroll
-      for (int q = 0; q < N; ++q) {
-        const float x = x_s[i + q];
+        for (int r = 0; r < GU_ROWS; ++r)
 #pragma unroll
-        for (int r = 0; r < GU_ROWS; ++r) {
-          ag[r] = fmaf(gv[r][q], x, ag[r]);
-          au[r] = fmaf(uv[r][q], x, au[r]);
+          for (int b = 0; b < PB; ++b) ag[r][b] = au[r][b] = 0.0f;
+        if (VEC) {
+          constexpr int N = Vec<TW>::N;
+          for (int i = lane * N; i < W; i += 32 * N) {
+            float gv[GU_ROWS][N], uv[GU_ROWS][N];
+#pragma unroll
+            for (int r = 0; r < GU_ROWS; ++r) {
+              const size_t off = (size_t)(f0 + r < F ? r : 0) * W + i;
+              Vec<TW>::load(g_rows + off, gv[r]);
+              Vec<TW>::load(u_rows + off, uv[r]);
+            }
+#pragma unroll
+            for (int b = 0; b < PB; ++b) {
+              if (b < nb) {
+#pragma unroll
+                for (int q = 0; q < N; ++q) {
+                  const float x = x_s[(size_t)b * W + i + q];
+#pragma unroll
+                  for (int r = 0; r < GU_ROWS; ++r) {
+                    ag[r][b] = fmaf(gv[r][q], x, ag[r][b]);
+                    au[r][b] = fmaf(uv[r][q], x, au[r][b]);
+                  }
+                }
+              }
+            }
+          }
+        } else {
+          for (int i = lane; i < W; i += 32) {
+#pragma unroll
+            for (int r = 0; r < GU_ROWS; ++r) {
+              const size_t off = (size_t)(f0 + r < F ? r : 0) * W + i;
+              const float g = jb::to_f32(g_rows[off]), u = jb::to_f32(u_rows[off]);
+#pragma unroll
+              for (int b = 0; b < PB; ++b) {
+                if (b < nb) {
+                  const float x = x_s[(size_t)b * W + i];
+                  ag[r][b] = fmaf(g, x, ag[r][b]);
+                  au[r][b] = fmaf(u, x, au[r][b]);
+                }
+              }
+            }
+          }
         }
-      }
-    }
-  } else {
-    for (int i = lane; i < W; i += 32) {
-      const float x = x_s[i];
 #pragma unroll
-      for (int r = 0; r < GU_ROWS; ++r) {
-        const size_t off = (size_t)(f0 + r < F ? r : 0) * W + i;
-        ag[r] = fmaf(jb::to_f32(g_rows[off]), x, ag[r]);
-        au[r] = fmaf(jb::to_f32(u_rows[off]), x, au[r]);
-      }
-    }
-  }
+        for (int r = 0; r < GU_ROWS; ++r)
 #pragma unroll
-  for (int r = 0; r < GU_ROWS; ++r) {
-    const float g = jb::warp_sum(ag[r]), u = jb::warp_sum(au[r]);
-    if (lane == 0 && f0 + r < F) act[(size_t)pair * F + f0 + r] = jb::gated(g, u, gate);
+          for (int b = 0; b < PB; ++b) {
+            if (b < nb) {
+              const float g = jb::warp_sum(ag[r][b]), u = jb::warp_sum(au[r][b]);
+              if (lane == 0 && f0 + r < F) act[(size_t)list[g0 + b] * F + f0 + r] = jb::gated(g, u, gate);
+            }
+          }
+      }
+      __syncthreads();                                   // the rows of x are free for the next pairs
+    }
   }
 }
 
 constexpr int DN_WARPS = 8, DN_ROWS = 4;
 
-// out[token of the pair][c] += Wd_e[c] . act[pair]
-template <typename TW, bool VEC>
+// out[token of the pair][c] += Wd_e[c] . act[pair], a block per (rows, expert) as above
+template <typename TW, bool VEC, int PB>
 __global__ void __launch_bounds__(DN_WARPS * 32) expert_down_kernel(
-    const float* __restrict__ act, const int* __restrict__ sel_e, int top, const TW* __restrict__ w_down,
+    const float* __restrict__ act, const int* __restrict__ sel_e, int top, int n_pairs, const TW* __restrict__ w_down,
     float* __restrict__ out, int W, int F) {
-  extern __shared__ __align__(16) float a_s[];
+  extern __shared__ __align__(16) float a_s[];           // [PB][F]
+  __shared__ int list[DN_WARPS * 32];
+  __shared__ int count;
   jb::pdl_launch_dependents();
   jb::pdl_wait();
-  const int pair = blockIdx.y, t = pair / top;
-  const int e = sel_e[pair];
-  for (int i = threadIdx.x; i < F; i += blockDim.x) a_s[i] = act[(size_t)pair * F + i];
-  __syncthreads();
+  const int e = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c0 = (blockIdx.x * DN_WARPS + warp) * DN_ROWS;
-  if (c0 >= W) return;
-  const TW* rows = w_down + ((size_t)e * W + c0) * F;
-  float acc[DN_ROWS];
-#pragma unroll
-  for (int r = 0; r < DN_ROWS; ++r) acc[r] = 0.0f;
-  if (VEC) {
-    constexpr int N = Vec<TW>::N;
-    for (int i = lane * N; i < F; i += 32 * N) {
-      float wv[DN_ROWS][N];
-#pragma unroll
-      for (int r = 0; r < DN_ROWS; ++r) Vec<TW>::load(rows + (size_t)(c0 + r < W ? r : 0) * F + i, wv[r]);
-#pragma unroll
-      for (int q = 0; q < N; ++q) {
-        const float a = a_s[i + q];
-#pragma unroll
-        for (int r = 0; r < DN_ROWS; ++r) acc[r] = fmaf(wv[r][q], a, acc[r]);
+  const TW* rows = w_down + ((size_t)e * W + min(c0, W - 1)) * F;
+  for (int base = 0; base < n_pairs; base += blockDim.x) {
+    const int n = pairs_of_expert(sel_e, n_pairs, base, e, list, &count);
+    for (int g0 = 0; g0 < n; g0 += PB) {
+      const int nb = min(PB, n - g0);
+      for (int b = 0; b < nb; ++b) {
+        const float* src = act + (size_t)list[g0 + b] * F;
+        for (int i = threadIdx.x; i < F; i += blockDim.x) a_s[(size_t)b * F + i] = src[i];
       }
-    }
-  } else {
-    for (int i = lane; i < F; i += 32) {
-      const float a = a_s[i];
+      __syncthreads();
+      if (c0 < W) {
+        float acc[DN_ROWS][PB];
 #pragma unroll
-      for (int r = 0; r < DN_ROWS; ++r)
-        acc[r] = fmaf(jb::to_f32(rows[(size_t)(c0 + r < W ? r : 0) * F + i]), a, acc[r]);
-    }
-  }
+        for (int r = 0; r < DN_ROWS; ++r)
 #pragma unroll
-  for (int r = 0; r < DN_ROWS; ++r) {
-    const float v = jb::warp_sum(acc[r]);
-    if (lane == 0 && c0 + r < W) {
-      if (top == 1) out[(size_t)t * W + c0 + r] += v;      // the token's only pair: nobody else adds here
-      else atomicAdd(out + (size_t)t * W + c0 + r, v);
+          for (int b = 0; b < PB; ++b) acc[r][b] = 0.0f;
+        if (VEC) {
+          constexpr int N = Vec<TW>::N;
+          for (int i = lane * N; i < F; i += 32 * N) {
+            float wv[DN_ROWS][N];
+#pragma unroll
+            for (int r = 0; r < DN_ROWS; ++r) Vec<TW>::load(rows + (size_t)(c0 + r < W ? r : 0) * F + i, wv[r]);
+#pragma unroll
+            for (int b = 0; b < PB; ++b) {
+              if (b < nb) {
+#pragma unroll
+                for (int q = 0; q < N; ++q) {
+                  const float a = a_s[(size_t)b * F + i + q];
+#pragma unroll
+                  for (int r = 0; r < DN_ROWS; ++r) acc[r][b] = fmaf(wv[r][q], a, acc[r][b]);
+                }
+              }
+            }
+          }
+        } else {
+          for (int i = lane; i < F; i += 32) {
+#pragma unroll
+            for (int r = 0; r < DN_ROWS; ++r) {
+              const float wgt = jb::to_f32(rows[(size_t)(c0 + r < W ? r : 0) * F + i]);
+#pragma unroll
+              for (int b = 0; b < PB; ++b)
+                if (b < nb) acc[r][b] = fmaf(wgt, a_s[(size_t)b * F + i], acc[r][b]);
+            }
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < DN_ROWS; ++r)
+#pragma unroll
+          for (int b = 0; b < PB; ++b) {
+            if (b < nb) {
+              const float v = jb::warp_sum(acc[r][b]);
+              if (lane == 0 && c0 + r < W) {
+                float* dst = out + (size_t)(list[g0 + b] / top) * W + c0 + r;
+                if (top == 1) *dst += v;                   // the token's only pair: nobody else adds here
+                else atomicAdd(dst, v);
+              }
+            }
+          }
+      }
+      __syncthreads();
     }
   }
 }
@@ -229,39 +300,63 @@ JB_EXPORT int jb_route_topk(const float* logits, int ld, int E, int top, int* se
   return (int)cudaLaunchKernelEx(&cfg.c, route_topk_kernel, logits, ld, E, top, sel_e, sel_w, T);
 }
 
-// h: [T, W] in x_dtype; the experts' weights in w_dtype; act: float32 scratch [T top, F]; out: float32 [T, W], added to.
+// h: [T, W] in x_dtype; the experts' weights ([E] of them) in w_dtype; act: float32 scratch [T top, F]; out: float32
+// [T, W], added to.
 JB_EXPORT int jb_experts_few_tokens(const void* h, int x_dtype, const int* sel_e, const float* sel_w, int top,
                                     const void* w_gate, const void* w_up, const void* w_down, int w_dtype, float* act,
-                                    float* out, int T, int W, int F, float gate_limit, float gate_alpha,
+                                    float* out, int T, int W, int F, int E, float gate_limit, float gate_alpha,
                                     cudaStream_t stream) {
   if (T <= 0) return 0;
   const int pairs = T * top;
-  JB_REFUSE((size_t)max(W, F) * sizeof(float) > 48 * 1024, "experts: rows of %d floats do not fit shared memory", max(W, F));
-  JB_REFUSE(pairs > 65535, "experts: %d (token, expert) pairs are too many for the few-token kernels", pairs);
+  JB_REFUSE(E < 1 || E > 65535, "experts: %d experts", E);
+  JB_REFUSE((size_t)max(W, F) * sizeof(float) > 96 * 1024, "experts: rows of %d floats do not fit shared memory", max(W, F));
+  // pairs served at once by a block: as many rows of x (or of act) as fit 96 KB of shared memory, four at most
+  const int pb = (size_t)max(W, F) * sizeof(float) * 4 <= 96 * 1024 ? 4 : (size_t)max(W, F) * sizeof(float) * 2 <= 96 * 1024 ? 2 : 1;
+  const size_t smem1 = (size_t)pb * W * sizeof(float), smem2 = (size_t)pb * F * sizeof(float);
   const jb::Gate gate{gate_limit, gate_alpha};
-  jb::Launch c1(dim3((F + GU_WARPS * GU_ROWS - 1) / (GU_WARPS * GU_ROWS), pairs), dim3(GU_WARPS * 32),
-                (size_t)W * sizeof(float), stream);
-  jb::Launch c2(dim3((W + DN_WARPS * DN_ROWS - 1) / (DN_WARPS * DN_ROWS), pairs), dim3(DN_WARPS * 32),
-                (size_t)F * sizeof(float), stream);
+  jb::Launch c1(dim3((F + GU_WARPS * GU_ROWS - 1) / (GU_WARPS * GU_ROWS), E), dim3(GU_WARPS * 32), smem1, stream);
+  jb::Launch c2(dim3((W + DN_WARPS * DN_ROWS - 1) / (DN_WARPS * DN_ROWS), E), dim3(DN_WARPS * 32), smem2, stream);
   cudaError_t e;
+#define JB_LAUNCH_GU(TW, TX, V, PB)                                                                                   \
+  do {                                                                                                                \
+    auto k = expert_gate_up_kernel<TW, TX, V, PB>;                                                                    \
+    if (smem1 > 48 * 1024) e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);      \
+    if (e == cudaSuccess)                                                                                             \
+      e = cudaLaunchKernelEx(&c1.c, k, (const TX*)h, sel_e, sel_w, top, pairs, (const TW*)w_gate, (const TW*)w_up,    \
+                             act, W, F, gate);                                                                        \
+  } while (0)
+#define JB_LAUNCH_DN(TW, V, PB)                                                                                       \
+  do {                                                                                                                \
+    auto k = expert_down_kernel<TW, V, PB>;                                                                           \
+    if (smem2 > 48 * 1024) e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);      \
+    if (e == cudaSuccess)                                                                                             \
+      e = cudaLaunchKernelEx(&c2.c, k, (const float*)act, sel_e, top, pairs, (const TW*)w_down, out, W, F);           \
+  } while (0)
 #define JB_LAUNCH_EX(TW, TX)                                                                                          \
   do {                                                                                                                \
     const bool v1 = W % Vec<TW>::N == 0 && aligned16((const TW*)w_gate) && aligned16((const TW*)w_up);                \
     const bool v2 = F % Vec<TW>::N == 0 && aligned16((const TW*)w_down);                                              \
-    e = v1 ? cudaLaunchKernelEx(&c1.c, expert_gate_up_kernel<TW, TX, true>, (const TX*)h, sel_e, sel_w, top,          \
-                                (const TW*)w_gate, (const TW*)w_up, act, W, F, gate)                                  \
-           : cudaLaunchKernelEx(&c1.c, expert_gate_up_kernel<TW, TX, false>, (const TX*)h, sel_e, sel_w, top,         \
-                                (const TW*)w_gate, (const TW*)w_up, act, W, F, gate);                                 \
+    e = cudaSuccess;                                                                                                  \
+    if (v1 && pb == 4) JB_LAUNCH_GU(TW, TX, true, 4);                                                                 \
+    else if (v1 && pb == 2) JB_LAUNCH_GU(TW, TX, true, 2);                                                            \
+    else if (v1) JB_LAUNCH_GU(TW, TX, true, 1);                                                                       \
+    else if (pb == 4) JB_LAUNCH_GU(TW, TX, false, 4);                                                                 \
+    else if (pb == 2) JB_LAUNCH_GU(TW, TX, false, 2);                                                                 \
+    else JB_LAUNCH_GU(TW, TX, false, 1);                                                                              \
     if (e != cudaSuccess) return (int)e;                                                                              \
-    e = v2 ? cudaLaunchKernelEx(&c2.c, expert_down_kernel<TW, true>, (const float*)act, sel_e, top, (const TW*)w_down, \
-                                out, W, F)                                                                            \
-           : cudaLaunchKernelEx(&c2.c, expert_down_kernel<TW, false>, (const float*)act, sel_e, top,                  \
-                                (const TW*)w_down, out, W, F);                                                        \
+    if (v2 && pb == 4) JB_LAUNCH_DN(TW, true, 4);                                                                     \
+    else if (v2 && pb == 2) JB_LAUNCH_DN(TW, true, 2);                                                                \
+    else if (v2) JB_LAUNCH_DN(TW, true, 1);                                                                           \
+    else if (pb == 4) JB_LAUNCH_DN(TW, false, 4);                                                                     \
+    else if (pb == 2) JB_LAUNCH_DN(TW, false, 2);                                                                     \
+    else JB_LAUNCH_DN(TW, false, 1);                                                                                  \
   } while (0)
   if (w_dtype == JB_F32 && x_dtype == JB_F32) JB_LAUNCH_EX(float, float);
   else if (w_dtype == JB_BF16 && x_dtype == JB_BF16) JB_LAUNCH_EX(bf16, bf16);
   else return JB_ERR_BAD_DTYPE;
 #undef JB_LAUNCH_EX
+#undef JB_LAUNCH_GU
+#undef JB_LAUNCH_DN
   return (int)e;
 }
 

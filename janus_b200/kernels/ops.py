@@ -66,7 +66,7 @@ _SIGNATURES = {
     "jb_join_norm": "pppppfpppfipipiiplplp", "jb_head_norm_gate": "ppipfipiiiip", "jb_sigmoid_gate": "pipiiiiip",
     "jb_head_norm_rope_cache": "pippfpippipppiiiiiiiip",
     "jb_delta_rule": "piiiipiiippfppllppiiiiip",
-    "jb_route_topk": "piiippip", "jb_experts_few_tokens": "pippipppippiiiffp", "jb_expert_gather": "pippipiip",
+    "jb_route_topk": "piiippip", "jb_experts_few_tokens": "pippipppippiiiiffp", "jb_expert_gather": "pippipiip",
     "jb_expert_scatter": "ppipiip",
     "jb_attention_tc_prefill": "pppppppiiiiiiiiiifpp", "jb_attention_tc_prefill_capped": "pppppppiiiiiiiiiififpp",
     "jb_streams_rmsnorm": "pppipifpiiipplp", "jb_streams_mix": "ppppiiip", "jb_streams_mix_rmsnorm": "pppppipifpiiiplp", "jb_embed_streams": "pippiiippp",
@@ -1512,8 +1512,9 @@ def route_topk(logits: torch.Tensor, top: int, sel_e: torch.Tensor, sel_w: torch
 def experts_few_tokens(h: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, w_gate: torch.Tensor,
                        w_up: torch.Tensor, w_down: torch.Tensor, act: torch.Tensor, out: torch.Tensor,
                        gate_limit: float = 0.0, gate_alpha: float = 1.0) -> None:
-    """out[t] += sum over the token's chosen experts e of Wd_e (act(Wg_e x) * (Wu_e x)) with x = weight * h[t]; the
-    experts' rows are streamed once per (token, expert) pair, sums in float32.  w_gate, w_up [E, F, W], w_down
+    """out[t] += sum over the token's chosen experts e of Wd_e (act(Wg_e x) * (Wu_e x)) with x = weight * h[t]; an
+    expert's rows are streamed once for up to four of the tokens that chose it (an expert nobody chose is not read),
+    sums in float32.  w_gate, w_up [E, F, W], w_down
     [E, W, F] in h's dtype; act: float32 scratch [T top, F]; out float32 [T, W]."""
     T, W = h.shape
     E, F, _ = w_gate.shape
@@ -1528,7 +1529,7 @@ def experts_few_tokens(h: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor
     _need(out, "experts' out", torch.float32, (T, W))
     _check(_lib("routed").jb_experts_few_tokens(
         _ptr(h), dtype_code(h.dtype), _ptr(sel_e), _ptr(sel_w), top, _ptr(w_gate), _ptr(w_up), _ptr(w_down),
-        dtype_code(w_gate.dtype), _ptr(act), _ptr(out), T, W, F, float(gate_limit), float(gate_alpha), _stream()),
+        dtype_code(w_gate.dtype), _ptr(act), _ptr(out), T, W, F, E, float(gate_limit), float(gate_alpha), _stream()),
         "experts_few_tokens", kernels=2)
 
 

@@ -5,9 +5,9 @@ float32 (the product's own accumulators), the scores s = sigmoid(z); a token's `
 largest scores (the lower index wins a tie) and their weights are those scores as they are, not renormalized.  The
 weight multiplies the expert's INPUT: out = sum over the chosen e of expert_e(s_e h).
 
-Steps of few (token, expert) pairs, every single-token step among them, stream each chosen expert's rows once per
-pair (`ops.experts_few_tokens`: two launches, float32 sums, nothing read back by the host, so the step can be
-recorded into a CUDA graph).  Prompt steps of the bfloat16 engine with more pairs read the choice back, gather the
+Steps of few (token, expert) pairs, every single-token step among them, stream each chosen expert's rows once for
+up to four of the tokens that chose it (`ops.experts_few_tokens`: two launches with a block per (rows, expert),
+float32 sums, nothing read back by the host, so the step can be recorded into a CUDA graph).  Prompt steps of the bfloat16 engine with more pairs read the choice back, gather the
 weighted rows expert by expert and run each expert's two products on the tensor cores over its rows; the results
 are added back token by token in the order of the token's choices.  The float32 engine always streams.
 """
