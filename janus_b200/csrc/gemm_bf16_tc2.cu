@@ -173,6 +173,8 @@ __host__ __device__ constexpr bool tokens_on_rows(int mode) { return mode == SWI
 struct TileCoord {
   int t0, f0;
   int k_lo, k_hi;   // k-tiles of this tile's slice of K (the whole of K unless an adding product is cut)
+  int t_end;        // tokens from here on are not written (T, or the end of the tile's group of rows)
+  int wf0;          // the weight row that meets output feature f0 (f0, or further down in a stack of matrices)
 };
 // Output tiles are numbered token tile fastest inside bands of TOK_BAND token tiles: the pairs that run at the
 // same time then work on a few token tiles times a few weight tiles, and a band's tokens (2,048 rows of X) stay
@@ -201,21 +203,35 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int n_tok_tiles, int n
 // from n_whole on are cut: the tiles that fill whole waves of pairs run uncut, and the last, partial wave is cut
 // into slices so that its pieces fill the pairs again (128 tiles on 74 pairs: 74 whole tiles, then 54 tiles in
 // 4 slices each = 216 pieces in three rounds of a quarter tile: 1.75 waves' time instead of 2).
+//
+// A grouped product (`table` given) takes its items from device memory instead: table[0] items, item i as the four
+// ints (t0, t_end, wf0, f0) at table[4 + 4 i].  The rows [t0, t_end) of X belong to one group (an expert's rows) and
+// meet the rows from wf0 on of a stack of weight matrices, one per group; the results land in columns f0... of Y.
+// A kernel earlier in the stream writes the table, so how many tiles there are is never known to the host.
 template <int MODE>
 struct Walk {
-  int n_items, n_tok_tiles, n_w_tiles, k_tiles, k_per, splits, n_pairs, n_whole;
+  int n_items, n_tok_tiles, n_w_tiles, k_tiles, k_per, splits, n_pairs, n_whole, T;
+  const int* table;
   int item;
   __device__ Walk(int pair, int n_pairs_, int n_items_, int n_tok_tiles_, int n_w_tiles_, int k_tiles_, int k_per_,
-                  int splits_, int n_whole_)
-      : n_items(n_items_), n_tok_tiles(n_tok_tiles_), n_w_tiles(n_w_tiles_), k_tiles(k_tiles_), k_per(k_per_),
-        splits(splits_), n_pairs(n_pairs_), n_whole(n_whole_), item(pair) {}
+                  int splits_, int n_whole_, int T_, const int* table_)
+      : n_items(table_ ? table_[0] : n_items_), n_tok_tiles(n_tok_tiles_), n_w_tiles(n_w_tiles_), k_tiles(k_tiles_),
+        k_per(k_per_), splits(splits_), n_pairs(n_pairs_), n_whole(n_whole_), T(T_), table(table_), item(pair) {}
   __device__ __forceinline__ bool next(TileCoord& c) {
     if (item >= n_items) return false;
+    if (table) {
+      const int4 e = *reinterpret_cast<const int4*>(table + 4 + 4 * (size_t)item);
+      c.t0 = e.x, c.t_end = e.y, c.wf0 = e.z, c.f0 = e.w;
+      c.k_lo = 0, c.k_hi = k_tiles;
+      item += n_pairs;
+      return true;
+    }
     if (item < n_whole) {
       c = tile_coord<MODE>(item, n_tok_tiles, n_w_tiles, k_tiles, k_tiles, 1);
     } else {
       c = tile_coord<MODE>(n_whole * splits + (item - n_whole), n_tok_tiles, n_w_tiles, k_tiles, k_per, splits);
     }
+    c.t_end = T, c.wf0 = c.f0;
     item += n_pairs;
     return true;
   }
@@ -227,7 +243,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
                                                            int T, int N_out, int ldy, int k_tiles, int n_tiles,
                                                            int n_tok_tiles, int k_per, int splits, int n_whole,
                                                            int up_tile_offset, RopeOut rope, jb::Gate gate,
-                                                           int* __restrict__ status) {
+                                                           const int* __restrict__ table, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
@@ -271,12 +287,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, n_w_tiles, k_tiles, k_per, splits, n_whole);
+      Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, n_w_tiles, k_tiles, k_per, splits, n_whole, T, table);
       TileCoord tc;
       while (ok && walk.next(tc)) {
         // rows of this CTA's two loads: its 128 rows of the pair's M side, its half of the column operand
         // this CTA's weight row tile (the weights are packed: a tile is one contiguous 16 KB block)
-        const int w_tile = MODE == SWIGLU ? (rank ? up_tile_offset + tc.f0 / BM : tc.f0 / BM) : tc.f0 / BM + (int)rank;
+        const int w_tile = MODE == SWIGLU ? (rank ? up_tile_offset + tc.wf0 / BM : tc.wf0 / BM) : tc.wf0 / BM + (int)rank;
         constexpr bool TOK_ROWS = tokens_on_rows(MODE);
         const int x_row = tc.t0 + (int)rank * BM;
         for (int i = tc.k_lo; i < tc.k_hi; ++i, ++it) {
@@ -303,7 +319,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
       constexpr uint32_t idesc = instr_desc_pair(BN);
       bool ok = true;
       int it = 0, j = 0;
-      Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, n_w_tiles, k_tiles, k_per, splits, n_whole);
+      Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, n_w_tiles, k_tiles, k_per, splits, n_whole, T, table);
       TileCoord tc;
       for (; ok && walk.next(tc); ++j) {
         const int buf = j & 1;
@@ -332,7 +348,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
     const int quarter = warp & 3;
     const int part = (warp - 2) >> 2;   // which of the columns' 16-wide chunks (every EPI_PARTS-th) this warp takes
     int j = 0;
-    Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, n_w_tiles, k_tiles, k_per, splits, n_whole);
+    Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, n_w_tiles, k_tiles, k_per, splits, n_whole, T, table);
     TileCoord tc;
     for (; walk.next(tc); ++j) {
       const int buf = j & 1;
@@ -351,7 +367,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
           tmem_ld16(lane_base + c0, r);
           tmem_ld16(lane_base + 128 + c0, u);
           tmem_ld_wait();
-          if (t < T) {
+          if (t < tc.t_end) {
             uint32_t packed[8];
 #pragma unroll
             for (int jj = 0; jj < 16; jj += 2) {
@@ -437,7 +453,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
         const bool f_ok = f < N_out;
 #pragma unroll 1
         for (int c0 = 16 * part; c0 < BN; c0 += 16 * EPI_PARTS) {
-          if (tc.t0 + c0 >= T) break;
+          if (tc.t0 + c0 >= tc.t_end) break;
           uint32_t r[16];
           tmem_ld16(lane_base + c0, r);
           tmem_ld_wait();
@@ -445,7 +461,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
 #pragma unroll
             for (int jj = 0; jj < 16; ++jj) {
               const int t = tc.t0 + c0 + jj;
-              if (t < T) {
+              if (t < tc.t_end) {
                 const float v = __uint_as_float(r[jj]);
                 const size_t o = (size_t)t * ldy + f;
                 if (MODE == STORE_BF16) {
@@ -529,7 +545,7 @@ int sm_count() {
 template <int MODE>
 int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T, int N_out, int K, int ldy,
            const RopeOut& rope, int* status, cudaStream_t stream, int split_k = 1, int whole_tiles = 0,
-           jb::Gate gate = jb::Gate{0.0f, 1.0f}) {
+           jb::Gate gate = jb::Gate{0.0f, 1.0f}, const int* table = nullptr, int max_items = 0) {
   constexpr int smem = STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -541,7 +557,9 @@ int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, 
   {
     const long long kt = (K + BK - 1) / BK, rt = (N_out + BM - 1) / BM;
     const long long need = MODE == SWIGLU ? (up_tile_offset + rt) * kt : rt * kt;
-    JB_REFUSE(w_tiles < need || (MODE == SWIGLU && up_tile_offset < rt) || w_tiles * BM > 0x7fffffffLL,
+    // (a grouped product's table names rows of a stack of matrices; whoever made the table answers for it, and
+    // a tile beyond the packed matrix reads zeros)
+    JB_REFUSE(((!table && w_tiles < need) || (MODE == SWIGLU && up_tile_offset < rt)) || w_tiles * BM > 0x7fffffffLL,
               "gemm_bf16_pair: the packed weight holds %lld tiles, the product needs %lld", w_tiles, need);
   }
   if (!make_packed_map(&mw, W, (uint64_t)w_tiles)) return JB_ERR_TENSORMAP;
@@ -560,7 +578,8 @@ int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, 
   const long long all_tiles = n_whole + (long long)(out_tiles_i - n_whole) * splits;
   JB_REFUSE(all_tiles > 0x7fffffffLL || (long long)n_tok_tiles * n_w_tiles > 0x7fffffffLL,
             "gemm_bf16_pair: too many tiles (%lld)", all_tiles);
-  const int n_tiles = (int)all_tiles;
+  // grouped: the table says how many items there are; the host only knows a bound, which sizes the grid
+  const int n_tiles = table ? max_items : (int)all_tiles;
   const int pairs = n_tiles < half_sms ? n_tiles : half_sms;
   cudaLaunchConfig_t cfg = cudaLaunchConfig_t{};
   cudaLaunchAttribute attrs[2];
@@ -581,7 +600,7 @@ int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, 
   }
   return (int)cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, mw, mx, Y, T, N_out, ldy, k_tiles, n_tiles,
                                  n_tok_tiles, k_per, splits, n_whole, MODE == SWIGLU ? up_tile_offset : 0, rope, gate,
-                                 status);
+                                 table, status);
 }
 
 }  // namespace
@@ -606,6 +625,28 @@ JB_EXPORT int jb_gemm_bf16_pair(const void* X, const void* W, long long w_tiles,
       return launch<SWIGLU>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream, 1, 0,
                             jb::Gate{gate_limit, gate_alpha});
     default: JB_REFUSE(true, "gemm_bf16_pair: unknown mode %d", mode);
+  }
+}
+
+// A grouped product: the rows of X [T, K] are sorted into groups (the tokens of one expert each), W is the packed
+// stack of the groups' matrices, and `table` (device memory, written earlier in the stream) lists the tiles: table[0]
+// items, item i = (t0, t_end, wf0, f0) at table[4 + 4 i]: the rows [t0, min(t0 + 256, t_end)) of X meet the weight
+// rows wf0 ... (a multiple of 128) and the results are columns f0 ... of Y [T, N_out] (row stride ldy).  `max_items`
+// bounds the table's items and sizes the grid.  Modes STORE_BF16, STORE_F32 and SWIGLU (W a stack of gated pairs:
+// all gate rows, then all up rows from tile up_tile_offset on; a tile is 128 features wide, else 256).
+JB_EXPORT int jb_gemm_bf16_pair_grouped(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y,
+                                        int T, int N_out, int K, int ldy, int mode, const int* table, int max_items,
+                                        float gate_limit, float gate_alpha, int* status, cudaStream_t stream) {
+  if (T <= 0 || N_out <= 0 || max_items <= 0) return 0;
+  JB_REFUSE(K <= 0 || K % 8 != 0, "gemm_bf16_pair_grouped: K = %d must be a positive multiple of 8", K);
+  JB_REFUSE(((uintptr_t)X | (uintptr_t)W | (uintptr_t)table) & 15, "gemm_bf16_pair_grouped: operands must be 16-byte aligned");
+  JB_REFUSE(!table, "gemm_bf16_pair_grouped: no table");
+  const jb::Gate gate{gate_limit, gate_alpha};
+  switch (mode) {
+    case STORE_BF16: return launch<STORE_BF16>(X, W, w_tiles, 0, Y, T, N_out, K, ldy, RopeOut{}, status, stream, 1, 0, gate, table, max_items);
+    case STORE_F32: return launch<STORE_F32>(X, W, w_tiles, 0, Y, T, N_out, K, ldy, RopeOut{}, status, stream, 1, 0, gate, table, max_items);
+    case SWIGLU: return launch<SWIGLU>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream, 1, 0, gate, table, max_items);
+    default: JB_REFUSE(true, "gemm_bf16_pair_grouped: mode %d is not one of store, swiglu", mode);
   }
 }
 

@@ -63,6 +63,9 @@ template <> struct Vec<float> {
     const float4 a = *reinterpret_cast<const float4*>(p);
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
   }
+  __device__ static void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
 };
 template <> struct Vec<bf16> {
   static constexpr int N = 8;
@@ -75,7 +78,18 @@ template <> struct Vec<bf16> {
       v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
   }
+  __device__ static void store(bf16* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
 };
+
+template <typename T> __host__ __device__ bool aligned16(const T* p) { return ((uintptr_t)p & 15) == 0; }
 
 constexpr int GU_WARPS = 8, GU_ROWS = 2;   // rows of gate (and of up) per warp
 
@@ -261,6 +275,55 @@ __global__ void __launch_bounds__(DN_WARPS * 32) expert_down_kernel(
   }
 }
 
+constexpr int PLAN_THREADS = 1024, PLAN_MAX_EXPERTS = 1024;
+
+// Sorts the (token, choice) pairs by expert and lists the tiles of the two grouped products, in one block, so that
+// the host never learns the router's choice.  order[place] = pair and where[pair] = place, an expert's pairs next
+// to each other (in no fixed order inside an expert: a row's result does not depend on its place).  A table holds
+// its count of items in [0] and item i as (t0, t_end, wf0, f0) at [4 + 4 i]: rows [t0, t_end) of the sorted pairs,
+// weight rows from wf0 on in the stack of the experts' matrices, output columns from f0 on.  Tiles are 256 rows;
+// `gu` tiles are 128 features of F wide, `dn` tiles 256 features of W.  Inside an expert the row tiles run fastest,
+// so CTAs that run side by side share a weight tile.
+__global__ void __launch_bounds__(PLAN_THREADS) expert_plan_kernel(const int* __restrict__ sel_e, int n_pairs, int E,
+                                                                   int F, int W, int* __restrict__ order,
+                                                                   int* __restrict__ where, int* __restrict__ gu,
+                                                                   int* __restrict__ dn) {
+  __shared__ int count[PLAN_MAX_EXPERTS], start[PLAN_MAX_EXPERTS], cursor[PLAN_MAX_EXPERTS], tiles_before[PLAN_MAX_EXPERTS];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&count[sel_e[i]], 1);
+  __syncthreads();
+  const int gu_per = (F + 127) / 128, dn_per = (W + 255) / 256;
+  if (threadIdx.x == 0) {
+    int rows = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = cursor[e] = rows;
+      tiles_before[e] = tiles;
+      rows += count[e];
+      tiles += (count[e] + 255) / 256;
+    }
+    gu[0] = tiles * gu_per;
+    dn[0] = tiles * dn_per;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int place = atomicAdd(&cursor[sel_e[i]], 1);
+    order[place] = i;
+    where[i] = place;
+  }
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int n_tt = (count[e] + 255) / 256, end = start[e] + count[e];
+    int4* g = reinterpret_cast<int4*>(gu + 4) + (size_t)tiles_before[e] * gu_per;
+    for (int ft = 0; ft < gu_per; ++ft)
+      for (int tt = 0; tt < n_tt; ++tt) g[ft * n_tt + tt] = make_int4(start[e] + tt * 256, end, e * F + ft * 128, ft * 128);
+    int4* d = reinterpret_cast<int4*>(dn + 4) + (size_t)tiles_before[e] * dn_per;
+    for (int ft = 0; ft < dn_per; ++ft)
+      for (int tt = 0; tt < n_tt; ++tt) d[ft * n_tt + tt] = make_int4(start[e] + tt * 256, end, e * W + ft * 256, ft * 256);
+  }
+}
+
 // rows[i] = weight[order[i]] * h[order[i] / top] in the products' dtype: the pairs (token, choice) in the order the
 // experts' products take them
 template <typename TX>
@@ -272,6 +335,17 @@ __global__ void expert_gather_kernel(const TX* __restrict__ h, const int* __rest
   const float s = sel_w[pair];
   const TX* src = h + (size_t)(pair / top) * W;
   TX* dst = rows + (size_t)blockIdx.x * W;
+  constexpr int N = Vec<TX>::N;
+  if (W % N == 0 && aligned16(h) && aligned16(rows)) {          // 16 bytes a thread
+    for (int i = threadIdx.x * N; i < W; i += blockDim.x * N) {
+      float v[N];
+      Vec<TX>::load(src + i, v);
+#pragma unroll
+      for (int q = 0; q < N; ++q) v[q] *= s;
+      Vec<TX>::store(dst + i, v);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = jb::from_f32<TX>(s * jb::to_f32(src[i]));
 }
 
@@ -281,6 +355,20 @@ __global__ void expert_scatter_kernel(const float* __restrict__ results, const i
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   const int t = blockIdx.x;
+  if (W % 4 == 0 && aligned16(results) && aligned16(out)) {     // 16 bytes a thread
+    for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      for (int k = 0; k < top; ++k) {
+        const float4 r = *reinterpret_cast<const float4*>(results + (size_t)where[(size_t)t * top + k] * W + i);
+        v.x += r.x, v.y += r.y, v.z += r.z, v.w += r.w;
+      }
+      float4* o = reinterpret_cast<float4*>(out + (size_t)t * W + i);
+      float4 a = *o;
+      a.x += v.x, a.y += v.y, a.z += v.z, a.w += v.w;
+      *o = a;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float v = 0.0f;
     for (int k = 0; k < top; ++k) v += results[(size_t)where[(size_t)t * top + k] * W + i];
@@ -288,7 +376,6 @@ __global__ void expert_scatter_kernel(const float* __restrict__ results, const i
   }
 }
 
-template <typename T> bool aligned16(const T* p) { return ((uintptr_t)p & 15) == 0; }
 
 }  // namespace
 
@@ -358,6 +445,16 @@ JB_EXPORT int jb_experts_few_tokens(const void* h, int x_dtype, const int* sel_e
 #undef JB_LAUNCH_GU
 #undef JB_LAUNCH_DN
   return (int)e;
+}
+
+// order, where: [pairs]; gu, dn: tables of the grouped products (4 ints and 4 more per item), see the kernel
+JB_EXPORT int jb_expert_plan(const int* sel_e, int pairs, int E, int F, int W, int* order, int* where, int* gu, int* dn,
+                             cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  JB_REFUSE(E < 1 || E > PLAN_MAX_EXPERTS, "expert_plan: %d experts (at most %d)", E, PLAN_MAX_EXPERTS);
+  JB_REFUSE(((uintptr_t)gu | (uintptr_t)dn) & 15, "expert_plan: tables must be 16-byte aligned");
+  jb::Launch cfg(dim3(1), dim3(PLAN_THREADS), 0, stream);
+  return (int)cudaLaunchKernelEx(&cfg.c, expert_plan_kernel, sel_e, pairs, E, F, W, order, where, gu, dn);
 }
 
 // rows: [pairs, W] in dtype, row i = weight[order[i]] * h[order[i] / top]

@@ -58,6 +58,7 @@ _SIGNATURES = {
     "jb_pack_weight_bf16": "piipp", "jb_rope_cache_write": "piipipppppiiiiiiip",
     "jb_gemm_f32": "pppiiiiiip", "jb_attention_f32": "pppppppiiiiiiififp",
     "jb_gemm_bf16": "pplipiiiiiiplpiffpp", "jb_gemm_bf16_pair": "pplipiiiiiiiffpp",
+    "jb_gemm_bf16_pair_grouped": "pplipiiiiipiffpp", "jb_expert_plan": "piiiippppp",
     "jb_gemm_bf16_pair_qkv_rope": "ppliippppppiiiipp",
     "jb_sample": "piipfiffppupppp",
     "jb_attention_bf16_prefill": "pppppppiiiiiiiifp", "jb_attention_bf16_decode": "ppppppppiiiiiiifip",
@@ -659,6 +660,47 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
         int(split_k), _ptr(partials), 0 if partials is None else partials.numel(), _ptr(tickets),
         0 if tickets is None else tickets.numel(), gate_limit, gate_alpha, _ptr(kernel_status(x.device)), _stream()),
         "gemm_bf16 " + label if label else "gemm_bf16")
+
+
+def grouped_max_items(rows: int, groups: int, features: int, mode: str) -> int:
+    """A bound on the tiles of a grouped product over `rows` rows in `groups` groups: every group's last tile of 256
+    rows may be partly empty."""
+    per = (features + 127) // 128 if mode == "swiglu" else (features + 255) // 256
+    return (rows // 256 + min(groups, rows)) * per
+
+
+def gemm_bf16_grouped(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, table: torch.Tensor, max_items: int,
+                      mode: str = "store", label: str = "", gate_limit: float = 0.0, gate_alpha: float = 1.0) -> None:
+    """A product per group of rows, all in one launch of the CTA-pair kernel: the rows of x [T, K] are sorted into
+    groups and w is the packed stack of the groups' matrices ([groups * N, K]; mode "swiglu": a gated pair of two
+    such stacks), N a multiple of 128.  `table` (int32 on the device, made by a kernel earlier in the stream, e.g.
+    `expert_plan`) holds its count of items in [0] and item i as (first row, end of the group's rows, first weight
+    row in the stack, first column of y) at [4 + 4 i]; `max_items` bounds the count (`grouped_max_items`).
+    y [T, N]: bfloat16 (mode "swiglu", or "store") or float32 ("store")."""
+    T, K = x.shape
+    _need(x, "grouped gemm x", torch.bfloat16)
+    _need(y, "grouped gemm y")
+    _need(table, "grouped gemm table", torch.int32)
+    if not isinstance(w, PackedWeight) or w.cols != K:
+        raise KernelError("grouped gemm: the weight must be packed and as wide as x")
+    N = y.shape[1]
+    if y.shape[0] != T or N % 128 or w.rows % N or table.numel() < 4 + 4 * max_items:
+        raise KernelError(f"grouped gemm: y {tuple(y.shape)}, a stack of {w.rows} rows, a table of {table.numel()} ints "
+                          f"for {max_items} items do not fit")
+    if mode == "swiglu":
+        code, want = 3, torch.bfloat16
+        if not w.up_tile_offset:
+            raise KernelError("grouped gemm swiglu: the weight is no gated pair")
+    elif mode == "store" and not w.up_tile_offset:
+        code, want = (1, torch.float32) if y.dtype == torch.float32 else (0, torch.bfloat16)
+    else:
+        raise KernelError(f"grouped gemm: mode {mode!r} does not fit the weight")
+    if y.dtype != want:
+        raise KernelError(f"grouped gemm {mode}: output must be {want}, got {y.dtype}")
+    name = "gemm_bf16_grouped " + label if label else "gemm_bf16_grouped"
+    _check(_lib("gemm_bf16_tc2", _defines_key(_PAIR_DEFINES), _PAIR_DEFINES).jb_gemm_bf16_pair_grouped(
+        _ptr(x), _ptr(w.tiles), w.n_tiles, w.up_tile_offset, _ptr(y), T, N, K, N, code, _ptr(table), int(max_items),
+        gate_limit, gate_alpha, _ptr(kernel_status(x.device)), _stream()), name)
 
 
 def gemm_qkv_rope_supported(T: int, hd: int) -> bool:
@@ -1531,6 +1573,27 @@ def experts_few_tokens(h: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor
         _ptr(h), dtype_code(h.dtype), _ptr(sel_e), _ptr(sel_w), top, _ptr(w_gate), _ptr(w_up), _ptr(w_down),
         dtype_code(w_gate.dtype), _ptr(act), _ptr(out), T, W, F, E, float(gate_limit), float(gate_alpha), _stream()),
         "experts_few_tokens", kernels=2)
+
+
+EXPERT_PLAN_MAX_EXPERTS = 1024
+
+
+def expert_plan(sel_e: torch.Tensor, experts: int, F: int, W: int, order: torch.Tensor, where: torch.Tensor,
+                gate_up_table: torch.Tensor, down_table: torch.Tensor) -> None:
+    """Sorts the (token, choice) pairs by expert on the device (order[place] = pair, where[pair] = place) and writes
+    the tile tables of the two grouped products (`gemm_bf16_grouped`): gate/up over stacks of F rows per expert in
+    tiles of 128 features, down over stacks of W rows per expert in tiles of 256."""
+    pairs = sel_e.numel()
+    _need(sel_e, "router's choice", torch.int32)
+    _need(order, "pair order", torch.int32, (pairs,))
+    _need(where, "pair places", torch.int32, (pairs,))
+    _need(gate_up_table, "gate/up table", torch.int32)
+    _need(down_table, "down table", torch.int32)
+    if (gate_up_table.numel() < 4 + 4 * grouped_max_items(pairs, experts, F, "swiglu")
+            or down_table.numel() < 4 + 4 * grouped_max_items(pairs, experts, W, "store")):
+        raise KernelError("expert_plan: a table is too small")
+    _check(_lib("routed").jb_expert_plan(_ptr(sel_e), pairs, int(experts), int(F), int(W), _ptr(order), _ptr(where),
+                                         _ptr(gate_up_table), _ptr(down_table), _stream()), "expert_plan")
 
 
 def expert_gather(h: torch.Tensor, order: torch.Tensor, sel_w: torch.Tensor, top: int, rows: torch.Tensor) -> None:

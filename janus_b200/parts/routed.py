@@ -7,9 +7,13 @@ weight multiplies the expert's INPUT: out = sum over the chosen e of expert_e(s_
 
 Steps of few (token, expert) pairs, every single-token step among them, stream each chosen expert's rows once for
 up to four of the tokens that chose it (`ops.experts_few_tokens`: two launches with a block per (rows, expert),
-float32 sums, nothing read back by the host, so the step can be recorded into a CUDA graph).  Prompt steps of the bfloat16 engine with more pairs read the choice back, gather the
-weighted rows expert by expert and run each expert's two products on the tensor cores over its rows; the results
-are added back token by token in the order of the token's choices.  The float32 engine always streams.
+float32 sums, nothing read back by the host, so the step can be recorded into a CUDA graph).  Prompt steps of the
+bfloat16 engine with more pairs sort the (token, choice) pairs by expert, gather the weighted rows in that order and
+run the experts' two products on the tensor cores over their rows; the results are added back token by token in the
+order of the token's choices.  Where the sizes allow it (width and inner width multiples of 128) the sort is a kernel
+(`ops.expert_plan`), and each of the two products is ONE launch over the stack of all experts' matrices whose tiles
+that kernel listed (`ops.gemm_bf16_grouped`): the host never reads the choice.  Other sizes read the choice back
+and launch each expert's products by themselves.  The float32 engine always streams.
 """
 from __future__ import annotations
 
@@ -40,6 +44,10 @@ class RoutedExperts(FeedForward):
         self.w_gate = self.w_up = self.w_down = None           # [E, F, W], [E, F, W], [E, W, F] row-major
         self.gate_up: List[GatedLinear] = []                   # bfloat16 engine: the experts' tensor-core products
         self.down: List[Linear] = []
+        # ... or, where tiles never straddle two experts, the packed stacks of all experts' matrices
+        self.grouped = (dtype == torch.bfloat16 and hidden_size % 128 == 0 and intermediate_size % 128 == 0
+                        and experts <= ops.EXPERT_PLAN_MAX_EXPERTS)
+        self.gate_up_stack = self.down_stack = None
 
     def weight_shapes(self):
         W, F = self.hidden_size, self.intermediate_size
@@ -62,7 +70,10 @@ class RoutedExperts(FeedForward):
 
         self.w_gate, self.w_up, self.w_down = stack("gate", (F, W)), stack("up", (F, W)), stack("down", (W, F))
         self.gate_up, self.down = [], []
-        if self.dtype == torch.bfloat16:
+        if self.grouped:
+            self.gate_up_stack = ops.pack_gated(self.w_gate.reshape(E * F, W), self.w_up.reshape(E * F, W))
+            self.down_stack = ops.pack_weight(self.w_down.reshape(E * W, F))
+        elif self.dtype == torch.bfloat16:
             for e in range(E):
                 gu = GatedLinear(W, F, self.dtype, self.device, name="expert_gate_up", pad_width=True)
                 gu.load(self.w_gate[e], self.w_up[e])
@@ -81,7 +92,10 @@ class RoutedExperts(FeedForward):
         ops.route_topk(logits, self.top, sel_e, sel_w)
         pairs = T * self.top
         if self.dtype == torch.bfloat16 and not ctx.is_decode and pairs > FEW_PAIRS:
-            self._by_expert(x, sel_e, sel_w, residual, ctx)
+            if self.grouped:
+                self._grouped(x, sel_e, sel_w, residual, ctx)
+            else:
+                self._by_expert(x, sel_e, sel_w, residual, ctx)
             return
         act = ws.get("experts_act", (pairs, self.intermediate_size), torch.float32)
         rows = max(1, MAX_STREAM_PAIRS // self.top)
@@ -89,6 +103,25 @@ class RoutedExperts(FeedForward):
             t1 = min(T, t0 + rows)
             ops.experts_few_tokens(x[t0:t1], sel_e[t0:t1], sel_w[t0:t1], self.w_gate, self.w_up, self.w_down,
                                    act[t0 * self.top: t1 * self.top], residual[t0:t1])
+
+    def _grouped(self, x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+        """The tensor-core path of a prompt step without the host: sort, gather, two grouped products, add back."""
+        T, W, F, E, top = x.shape[0], self.hidden_size, self.intermediate_size, self.experts, self.top
+        pairs = T * top
+        ws = ctx.workspace
+        max_gu = ops.grouped_max_items(pairs, E, F, "swiglu")
+        max_dn = ops.grouped_max_items(pairs, E, W, "store")
+        index = ws.get("experts_index", (2, pairs), torch.int32)
+        table_gu = ws.get("experts_gate_up_tiles", (4 + 4 * max_gu,), torch.int32)
+        table_dn = ws.get("experts_down_tiles", (4 + 4 * max_dn,), torch.int32)
+        ops.expert_plan(sel_e, E, F, W, index[0], index[1], table_gu, table_dn)
+        rows = ws.get("experts_rows", (pairs, W), self.dtype)
+        ops.expert_gather(x, index[0], sel_w, top, rows)
+        act = ws.get("experts_act_rows", (pairs, F), self.dtype)
+        ops.gemm_bf16_grouped(rows, self.gate_up_stack, act, table_gu, max_gu, mode="swiglu", label="expert_gate_up")
+        results = ws.get("experts_results", (pairs, W), torch.float32)
+        ops.gemm_bf16_grouped(act, self.down_stack, results, table_dn, max_dn, mode="store", label="expert_down")
+        ops.expert_scatter(results, index[1], top, residual)
 
     def _by_expert(self, x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         """The tensor-core path of a prompt step: the host reads the choice, sorts the (token, choice) pairs by expert

@@ -66,10 +66,11 @@ CFG_B = dict(architecture="Mugedra", vocab=200, width=96, norm=dict(eps=1e-6),
 CFG_C = dict(architecture="Mugedra", vocab=75, width=36, norm=dict(eps=1e-5), loop=dict(start=0, stop=1, times=2),
              layers=[layer(left(2, 1, 10, 7, 0.3, softcap=3.0, mask=33, rot=(6, 100.0)), right(3, 1, 5, 9, 3), (13, 4, 2)),
                      layer(left(3, 3, 6, 11, 0.4, mask=9), right(2, 2, 7, 5, 2), (22, 3, 1))])
-# sizes that the tensor-core kernels take; the whole model is the loop
+# sizes that the tensor-core kernels take (the first layer's experts as grouped products, the second's one by one);
+# the whole model is the loop
 CFG_D = dict(architecture="Mugedra", vocab=128, width=128, norm=dict(eps=1e-5), loop=dict(start=0, stop=2, times=2),
              layers=[layer(left(8, 2, 32, 32, 0.18, softcap=20.0, mask=100, rot=(32, 250000.0, (8.0, 128, 32.0, 1.0))),
-                           right(4, 2, 32, 32, 4), (64, 8, 2)),
+                           right(4, 2, 32, 32, 4), (128, 8, 2)),
                      layer(left(4, 4, 64, 64, 0.125, mask=192, rot=(16, 10000.0)), right(2, 1, 64, 64, 4), (32, 4, 3))])
 CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D}
 TAGS = 4          # features that carry a token's class for the routers (see `decisive`)
@@ -421,6 +422,59 @@ def test_router_and_expert_kernels_against_the_plain_feed_forward():
         ops.expert_scatter(results.cuda(), torch.from_numpy(where).cuda(), top, acc)
         want_acc = torch.stack([sum(results[where[t * top + j]].to(P.DT) for j in range(top)) for t in range(T)])
         assert rel_err(acc.cpu(), want_acc) < 1e-6
+
+
+@gpu
+@pytest.mark.parametrize("T,W,F,E,top,skip", [(700, 128, 256, 5, 2, 3), (260, 256, 128, 3, 1, None), (90, 128, 128, 40, 3, 0)])
+def test_experts_of_a_prompt_sorted_on_the_device_and_served_by_two_grouped_products(T, W, F, E, top, skip):
+    """Pairs sorted by expert without the host, the experts' products as one launch each over stacked matrices:
+    experts with more rows than a tile, with a few rows, with none."""
+    from janus_b200.kernels import ops
+    g = torch.Generator().manual_seed(11)
+    wts = {"router": torch.randn(E, W, generator=g).to(torch.bfloat16).to(P.DT)}
+    if skip is not None:
+        wts["router"][skip] = 0.0
+        wts["router"][skip, 0] = -50.0                      # with h[:, 0] = 1 nobody chooses this expert
+    for x in range(E):
+        wts[f"e{x}.gate"] = (torch.randn(F, W, generator=g) * W ** -0.5).to(torch.bfloat16).to(P.DT)
+        wts[f"e{x}.up"] = (torch.randn(F, W, generator=g) * W ** -0.5).to(torch.bfloat16).to(P.DT)
+        wts[f"e{x}.down"] = (torch.randn(W, F, generator=g) * F ** -0.5).to(torch.bfloat16).to(P.DT)
+    h = torch.randn(T, W, generator=g)
+    h[:, 0] = 1.0
+    h = h.to(torch.bfloat16)
+    want = P.routed_feed_forward(h.to(P.DT), wts, E, top)
+    z = (h.to(P.DT) @ wts["router"].T).float().cuda()
+    sel_e = torch.empty(T, top, dtype=torch.int32, device="cuda")
+    sel_w = torch.empty(T, top, device="cuda")
+    ops.route_topk(z, top, sel_e, sel_w)
+    pairs = T * top
+    max_gu, max_dn = ops.grouped_max_items(pairs, E, F, "swiglu"), ops.grouped_max_items(pairs, E, W, "store")
+    index = torch.full((2, pairs), -1, dtype=torch.int32, device="cuda")
+    t_gu = torch.zeros(4 + 4 * max_gu, dtype=torch.int32, device="cuda")
+    t_dn = torch.zeros(4 + 4 * max_dn, dtype=torch.int32, device="cuda")
+    ops.expert_plan(sel_e, E, F, W, index[0], index[1], t_gu, t_dn)
+    order, where, chosen = index[0].cpu(), index[1].cpu(), sel_e.reshape(-1).cpu()
+    assert sorted(order.tolist()) == list(range(pairs))
+    assert where[order.long()].tolist() == list(range(pairs))
+    in_order = chosen[order.long()]
+    assert bool((in_order[1:] >= in_order[:-1]).all())           # an expert's pairs lie next to each other
+    if skip is not None:
+        assert skip not in set(chosen.tolist())
+    counts = torch.bincount(chosen.long(), minlength=E)
+    tiles = int(((counts + 255) // 256).sum())
+    assert int(t_gu[0]) == tiles * (F // 128) <= max_gu and int(t_dn[0]) == tiles * ((W + 255) // 256) <= max_dn
+    stack = lambda kind: torch.cat([wts[f"e{x}.{kind}"] for x in range(E)]).to(torch.bfloat16).cuda().contiguous()  # noqa: E731
+    gate_up, down = ops.pack_gated(stack("gate"), stack("up")), ops.pack_weight(stack("down"))
+    rows = torch.empty(pairs, W, dtype=torch.bfloat16, device="cuda")
+    ops.expert_gather(h.cuda(), index[0], sel_w, top, rows)
+    act = torch.full((pairs, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_bf16_grouped(rows, gate_up, act, t_gu, max_gu, mode="swiglu")
+    results = torch.full((pairs, W), float("nan"), device="cuda")
+    ops.gemm_bf16_grouped(act, down, results, t_dn, max_dn, mode="store")
+    out = torch.zeros(T, W, device="cuda")
+    ops.expert_scatter(results, index[1], top, out)
+    ops.check_kernel_status(torch.device("cuda"))
+    assert rel_err(out.cpu(), want) < 1e-2
 
 
 @gpu
