@@ -332,7 +332,8 @@ def _run_delta_kernels(u, raw, conv_w, a_log, dt_bias, state, lengths, slots, H,
 
 @gpu
 @pytest.mark.parametrize("H,G,d,e,taps", [(4, 2, 8, 16, 3), (3, 1, 5, 9, 2), (2, 2, 64, 64, 4), (1, 1, 200, 24, 1),
-                                          (6, 3, 32, 40, 5)])
+                                          (6, 3, 32, 40, 5), (2, 1, 96, 40, 3), (2, 2, 128, 128, 4), (1, 1, 65, 17, 2),
+                                          (1, 1, 256, 16, 2)])
 def test_convolution_and_delta_rule_kernels_against_the_plain_recurrence(H, G, d, e, taps):
     """Three sequences of unequal lengths in slots out of order: a prompt step, a second portion from the state the
     first left, then single tokens; outputs and the final state against the plain recurrence run in one piece."""
@@ -731,6 +732,79 @@ def test_portions_then_single_tokens_in_a_batch_and_slots_used_again(tmp_path, n
                 model.free_slot(slots[i])
                 live.remove(i)
         model.engine.cache.check()
+    model.check()
+
+
+def drawn_config(seed):
+    """A configuration drawn from a seed: sizes from small and odd to those of the tensor-core kernels, every
+    optional constant present or absent, layers with and without a feed-forward, a loop anywhere or none."""
+    import random
+    rng = random.Random(seed)
+    n_layers = rng.choice([1, 2, 3, 4])
+    width = rng.choice([40, 64, 96, 128, 192, 256])
+    layers = []
+    for _ in range(n_layers):
+        kv = rng.choice([1, 2, 3])
+        dim = rng.choice([8, 16, 24, 32, 64, 128])
+        vdim = rng.choice([dim, dim, 8, 16, 32, 64])
+        rot = None
+        if rng.random() < 0.75:
+            dims = rng.choice([dim, dim // 2, max(2, dim // 4 * 2)])
+            rot = (dims, rng.choice([50.0, 10000.0, 250000.0]))
+            if rng.random() < 0.6:
+                rot += ((rng.choice([2.0, 4.0, 8.0]), rng.choice([16, 64, 128]), rng.choice([4.0, 32.0]), 1.0),)
+        a = left(kv * rng.choice([1, 2, 4]), kv, dim, vdim, rng.choice([dim ** -0.5, 0.2, 0.4]),
+                 softcap=rng.choice([None, 3.0, 50.0]), mask=rng.choice([None, 3, 16, 41, 64, 100, 128]), rot=rot)
+        g = rng.choice([1, 2])
+        r = right(g * rng.choice([1, 2, 3]), g, rng.choice([8, 16, 48, 72, 96, 128]), rng.choice([8, 16, 40, 64]),
+                  rng.choice([1, 2, 3, 4]))
+        moe = None
+        if rng.random() < 0.8:
+            experts = rng.choice([1, 2, 4, 7, 8])
+            moe = (rng.choice([24, 64, 128]), experts, rng.choice([t for t in (1, 2, 3) if t <= experts]))
+        layers.append(layer(a, r, moe))
+    cfg = dict(architecture="Mugedra", vocab=rng.choice([97, 256, 500]), width=width,
+               norm=dict(eps=rng.choice([1e-5, 1e-6])), layers=layers)
+    if rng.random() < 0.7:
+        start = rng.randrange(n_layers)
+        cfg["loop"] = dict(start=start, stop=rng.randrange(start + 1, n_layers + 1), times=rng.choice([1, 2, 3]))
+    return cfg
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", list(range(1, 25)))
+def test_configurations_drawn_from_a_seed(tmp_path, seed, dtype):
+    """Three prompts of unequal length in one step, a second portion each, then token by token while the shorter
+    requests end, against the plain implementation's logits of the whole sequences."""
+    from janus_b200.engine import StepEntry
+    cfg = drawn_config(seed)
+    w = weights_for(cfg, 40 + seed)
+    for name in [n for n in w if n.endswith(".mlp.router")]:       # wide models: the class decides, not the rest
+        w[name][:, :cfg["width"] - TAGS] *= 0.25
+    d = P.save_folder(cfg, w, str(tmp_path / f"drawn{seed}"))
+    tol = tol_for(dtype)
+    model = load(d, dtype, max_tokens=1024, max_slots=3)
+    seqs = [random_tokens(n, cfg["vocab"], 300 + 10 * seed + n) for n in (170, 9, 77)]
+    ref = [plain_logits(cfg, w, ids) for ids in seqs]
+    slots = [model.alloc_slot() for _ in seqs]
+    at = [0, 0, 0]
+    for portion in ((131, 2, 40), (30, 3, 33)):
+        out = model.step([StepEntry(slots[i], seqs[i][at[i]:at[i] + n], range(n)) for i, n in enumerate(portion)]).cpu()
+        row = 0
+        for i, n in enumerate(portion):
+            assert rel_err(out[row:row + n], ref[i][at[i]:at[i] + n]) < tol, (cfg, i, at[i], n)
+            row += n
+            at[i] += n
+    live = [0, 1, 2]
+    while live:
+        out = model.step([StepEntry(slots[i], [seqs[i][at[i]]], [0]) for i in live]).cpu()
+        for row, i in enumerate(live):
+            assert rel_err(out[row:row + 1], ref[i][at[i]:at[i] + 1]) < tol, (cfg, i, at[i])
+            at[i] += 1
+        for i in [i for i in live if at[i] == len(seqs[i])]:
+            model.free_slot(slots[i])
+            live.remove(i)
     model.check()
 
 
