@@ -391,7 +391,10 @@ def test_router_and_expert_kernels_against_the_plain_feed_forward():
     assert sel_e.cpu().tolist() == [[1, 2, 4], [0, 4, 2]]
     assert rel_err(sel_w.cpu(), torch.sigmoid(torch.tensor([[2.0, 2.0, 2.0], [3.0, 1.0, 0.0]]))) < 1e-6
     for T, W, F, E, top, dtype in ((9, 64, 48, 5, 2, torch.float32), (1, 36, 13, 4, 4, torch.float32),
-                                   (33, 96, 40, 7, 1, torch.float32), (20, 64, 32, 6, 3, torch.bfloat16)):
+                                   (33, 96, 40, 7, 1, torch.float32), (20, 64, 32, 6, 3, torch.bfloat16),
+                                   # inner widths that the down product takes in parts
+                                   (5, 32, 2100, 3, 1, torch.float32), (6, 40, 4500, 2, 2, torch.bfloat16),
+                                   (3, 64, 4096, 2, 1, torch.bfloat16)):
         wts = {"router": torch.randn(E, W, generator=g).to(torch.bfloat16).to(P.DT)}
         for x in range(E):
             wts[f"e{x}.gate"] = (torch.randn(F, W, generator=g) * W ** -0.5).to(torch.bfloat16).to(P.DT)
