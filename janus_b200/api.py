@@ -187,7 +187,7 @@ _WHOLE = object()        # max_step_tokens left at the engine's default
 
 
 def _build(config_dict: dict, checkpoint_factory, dtype, max_tokens: int, max_seq_len: Optional[int],
-           max_slots: Optional[int], device, use_graphs: bool, max_step_tokens=_WHOLE) -> Model:
+           max_slots: Optional[int], device, use_graphs: bool, max_step_tokens=_WHOLE, shape_of=None) -> Model:
     if not torch.cuda.is_available():
         raise RuntimeError("janus_b200 needs a CUDA device (sm_100a); there is no CPU path")
     device = torch.device(device)
@@ -196,6 +196,9 @@ def _build(config_dict: dict, checkpoint_factory, dtype, max_tokens: int, max_se
     torch_dtype = parse_dtype(dtype)
     arch = resolve_architecture(config_dict)
     config = arch.config_class.from_dict(config_dict)
+    if shape_of is not None and hasattr(config, "with_tensor_shapes"):
+        # a design may leave a size to the shape of a tensor (the rank of a low-rank projection)
+        config = config.with_tensor_shapes(shape_of)
     with torch.cuda.device(device):
         model = arch.build(config, torch_dtype, device)
         model.load(checkpoint_factory(arch, config))
@@ -221,8 +224,11 @@ def load(model_dir: str, dtype="bfloat16", max_tokens: int = 8192, max_seq_len: 
     `max_tokens` sizes the cache: the most tokens live sequences hold at any
     time, each sequence rounded up to a multiple of 64.  `max_step_tokens`: `generate` cuts a batch's
     prompts into steps of at most that many tokens (default 32,768; None: one step whatever the size)."""
-    return _build(read_config_json(model_dir), lambda arch, config: FolderCheckpoint(model_dir), dtype,
-                  max_tokens, max_seq_len, max_slots, device, use_graphs, max_step_tokens)
+    checkpoint = FolderCheckpoint(model_dir)
+    names = set(checkpoint.names())
+    return _build(read_config_json(model_dir), lambda arch, config: checkpoint, dtype,
+                  max_tokens, max_seq_len, max_slots, device, use_graphs, max_step_tokens,
+                  shape_of=lambda name: checkpoint.shape(name) if name in names else None)
 
 
 def load_random(config_dict: dict, seed: int, dtype="bfloat16", max_tokens: int = 8192,

@@ -153,10 +153,12 @@ __device__ __forceinline__ void qk_product(float (&s)[NT][4], const bf16* q_rows
 // (negative = row unused); keys outside [row_lo, row_pos] are masked.
 // chunk > 0: a query sees only the keys of its own chunk of positions, [floor(pos / chunk) chunk, pos];
 // cap_log2 > 0: scores are capped, s -> cap tanh(s scale / cap), with cap_log2 = cap log2(e), inv_cap = scale / cap.
+// sink = 1: the softmax's denominator has one more term, exp(0) (a key of score 0 that has no value).
 struct Cap {
   int chunk;
   float cap_log2;
   float inv_cap;
+  float sink;
 };
 __device__ __forceinline__ int chunk_lo(int lo, int pos, int chunk) {
   return (chunk > 0 && pos >= 0) ? max(lo, (pos / chunk) * chunk) : lo;
@@ -304,6 +306,7 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
     const int row = warp * 16 + (lane >> 2) + 8 * r;
     const int tl = row / G;
     if (tl < n_tok) {
+      if (cap.sink > 0.0f) l += cap.sink * exp2f(st.m[r] == -CUDART_INF_F ? 0.0f : -st.m[r]);
       const float inv = 1.0f / l;
       bf16* o = out + ((size_t)(qs + tok0 + tl) * nh + kvh * G + row % G) * HD + 2 * (lane & 3);
 #pragma unroll
@@ -520,6 +523,7 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
     }
     const int head = kvh * G + g0 + row;
     if (n_splits == 1) {
+      if (cap.sink > 0.0f) l += cap.sink * exp2f(-m_use);
       out[((size_t)seq * nh + head) * HD + d] = __float2bfloat16_rn(o / l);
     } else {
       const size_t base = ((size_t)seq * nh + head) * n_splits + split;
@@ -533,7 +537,7 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
 }
 
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                      bf16* __restrict__ out, int n_splits) {
+                                      bf16* __restrict__ out, int n_splits, float sink) {
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   const size_t item = blockIdx.x;  // seq * nh + head
@@ -547,6 +551,7 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
       o += part_o[(item * n_splits + s) * HD + d] * f;
       l += ml[2 * s + 1] * f;
     }
+    if (sink > 0.0f) l += sink * exp2f(m == -CUDART_INF_F ? 0.0f : -m);
     out[item * HD + d] = __float2bfloat16_rn(o / l);
   }
 }
@@ -625,8 +630,8 @@ cudaError_t decode_dispatch(dim3 grid, cudaStream_t stream, bool pdl, const bf16
 JB_EXPORT int jb_attention_bf16_head_dim() { return HD; }
 
 namespace {
-Cap make_cap(int chunk, float softcap, float scale) {
-  return softcap > 0.0f ? Cap{chunk, softcap * LOG2E, scale / softcap} : Cap{chunk, 0.0f, 0.0f};
+Cap make_cap(int chunk, float softcap, float scale, float sink) {
+  return softcap > 0.0f ? Cap{chunk, softcap * LOG2E, scale / softcap, sink} : Cap{chunk, 0.0f, 0.0f, sink};
 }
 
 int prefill_launch(const void* q, const void* k_cache, const void* v_cache, void* out,
@@ -663,14 +668,15 @@ JB_EXPORT int jb_attention_bf16_prefill(const void* q, const void* k_cache, cons
 }
 
 // As jb_attention_bf16_prefill, with a chunked mask (chunk > 0: a query sees only the keys of its own chunk of
-// positions) and capped scores (softcap > 0: s -> softcap tanh(s / softcap)).
+// positions), capped scores (softcap > 0: s -> softcap tanh(s / softcap)) and a sink (sink = 1: one more term exp(0)
+// in the softmax's denominator).
 JB_EXPORT int jb_attention_bf16_prefill_capped(const void* q, const void* k_cache, const void* v_cache, void* out,
                                                const int* block_table, const int* q_start, const int* kv_len,
                                                int n_seqs, int max_q_len, int nh, int nkv, int hd, int page_size,
                                                int max_pages, int window, float scale, int chunk, float softcap,
-                                               cudaStream_t stream) {
+                                               float sink, cudaStream_t stream) {
   return prefill_launch(q, k_cache, v_cache, out, block_table, q_start, kv_len, n_seqs, max_q_len, nh, nkv, hd,
-                        page_size, max_pages, window, scale, make_cap(chunk, softcap, scale), stream);
+                        page_size, max_pages, window, scale, make_cap(chunk, softcap, scale, sink), stream);
 }
 
 // Scratch (when n_splits > 1): part_o float32 [n_seqs * nh * n_splits * hd], part_ml float32
@@ -695,7 +701,7 @@ int decode_launch(const void* q, const void* k_cache, const void* v_cache, void*
   if (n_splits > 1) {
     jb::Launch cfg2(dim3(n_seqs * nh), dim3(HD >= 128 ? 128 : 64), 0, stream);
     le = cudaLaunchKernelEx(&cfg2.c, decode_combine_kernel, (const float*)part_o, (const float*)part_ml, (bf16*)out,
-                            n_splits);
+                            n_splits, cap.sink);
     if (le != cudaSuccess) return (int)le;
   }
   return 0;
@@ -716,10 +722,10 @@ JB_EXPORT int jb_attention_bf16_decode_capped(const void* q, const void* k_cache
                                               float* part_o, float* part_ml, const int* block_table,
                                               const int* kv_len, int n_seqs, int nh, int nkv, int hd, int page_size,
                                               int max_pages, int window, float scale, int n_splits, int chunk,
-                                              float softcap, cudaStream_t stream) {
+                                              float softcap, float sink, cudaStream_t stream) {
   return decode_launch(q, k_cache, v_cache, out, part_o, part_ml, block_table, kv_len, n_seqs, nh, nkv, hd,
                        page_size, max_pages, window, scale, n_splits, FusedInput{}, stream,
-                       make_cap(chunk, softcap, scale));
+                       make_cap(chunk, softcap, scale, sink));
 }
 
 // As jb_attention_bf16_decode, but q, k and v of the new tokens come as the projection's float32
@@ -800,7 +806,7 @@ JB_EXPORT int jb_attention_bf16_decode_noalloc(const void* q, const void* k_cach
                       FusedInput{});
   if (e != cudaSuccess) return (int)e;
   if (n_splits > 1) {
-    decode_combine_kernel<<<n_seqs * nh, HD >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (bf16*)out, n_splits);
+    decode_combine_kernel<<<n_seqs * nh, HD >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (bf16*)out, n_splits, 0.0f);
     JB_CHECK_LAUNCH();
   }
   return 0;

@@ -2,7 +2,8 @@
 // alike: one warp per (token, query head); the token attends to the keys of
 // its own sequence at positions [max(0, pos-window+1), pos] (window 0 = all);
 // with chunk > 0 only to those of them that lie in its own chunk of positions,
-// [floor(pos/chunk) chunk, pos]; with softcap > 0 a score s becomes softcap tanh(s/softcap).
+// [floor(pos/chunk) chunk, pos]; with softcap > 0 a score s becomes softcap tanh(s/softcap); with sink = 1 the
+// softmax's denominator has one more term, exp(0): a key of score 0 that has no value.
 // Formulas: crates/janus-engine/src/compute/shaders/attention.wgsl:96-115
 // (kv head = h*nkv/nh, score = dot * scale), softmax.wgsl:29-50 (exp(s-max)/sum),
 // attention.wgsl:170-185 (sum of p*v).  The softmax runs online over chunks of
@@ -27,7 +28,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_f32_kernel(
     const float* __restrict__ q, const float* __restrict__ k_cache, const float* __restrict__ v_cache,
     float* __restrict__ out, const int* __restrict__ block_table, const int* __restrict__ token_slot,
     const int* __restrict__ positions, int T, int nh, int nkv, int hd, int page_size, int max_pages,
-    int window, float scale, int chunk, float softcap) {
+    int window, float scale, int chunk, float softcap, float sink) {
   __shared__ __align__(16) float q_s[WARPS][MAX_HD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_f32_kernel(
     }
     m = m_new;
   }
+  if (sink > 0.0f) l += sink * expf(m == -CUDART_INF_F ? 0.0f : -m);
   float* o = out + ((size_t)t * nh + h) * hd;
 #pragma unroll
   for (int j = 0; j < MAX_HD / 32; ++j) {
@@ -122,7 +124,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_f32_kernel(
 JB_EXPORT int jb_attention_f32(const float* q, const float* k_cache, const float* v_cache, float* out,
                                const int* block_table, const int* token_slot, const int* positions, int T,
                                int nh, int nkv, int hd, int page_size, int max_pages, int window, float scale,
-                               int chunk, float softcap, cudaStream_t stream) {
+                               int chunk, float softcap, float sink, cudaStream_t stream) {
   if (T <= 0) return 0;
   JB_REFUSE(hd > MAX_HD || hd <= 0, "attention_f32: head_dim %d is outside (0, %d]", hd, MAX_HD);
   JB_REFUSE(nkv <= 0 || nh % nkv != 0, "attention_f32: %d heads are not a multiple of %d kv heads", nh, nkv);
@@ -131,11 +133,11 @@ JB_EXPORT int jb_attention_f32(const float* q, const float* k_cache, const float
   if (hd % 4 == 0 && (((uintptr_t)k_cache) & 15) == 0)
     attention_f32_kernel<true><<<blocks, WARPS * 32, 0, stream>>>(q, k_cache, v_cache, out, block_table, token_slot,
                                                                   positions, T, nh, nkv, hd, page_size, max_pages,
-                                                                  window, scale, chunk, softcap);
+                                                                  window, scale, chunk, softcap, sink);
   else
     attention_f32_kernel<false><<<blocks, WARPS * 32, 0, stream>>>(q, k_cache, v_cache, out, block_table, token_slot,
                                                                    positions, T, nh, nkv, hd, page_size, max_pages,
-                                                                   window, scale, chunk, softcap);
+                                                                   window, scale, chunk, softcap, sink);
   JB_CHECK_LAUNCH();
   return 0;
 }

@@ -272,9 +272,10 @@ __device__ __forceinline__ void scale16(uint32_t* r, float f) {
 // A chunked mask and capped scores.  chunk > 0: a query sees only the keys of its own chunk of positions,
 // [floor(pos / chunk) chunk, pos].  cap_s > 0: a raw score s becomes cap_s tanh(s inv_cap), with cap_s = cap / scale
 // and inv_cap = scale / cap, so that the scale applied afterwards gives cap tanh(s scale / cap).
+// sink = 1: the softmax's denominator has one more term, exp(0) (a key of score 0 that has no value).
 struct Cap {
   int chunk;
-  float cap_s, inv_cap;
+  float cap_s, inv_cap, sink;
 };
 __device__ __forceinline__ int chunk_lo(int lo, int pos, int chunk) {
   return (chunk > 0 && pos >= 0) ? max(lo, (pos / chunk) * chunk) : lo;
@@ -497,6 +498,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
     if (ok && nb > 0) ok = mbar_wait(o_done(w), 0, status, 13);
     if (ok) {
       tc_fence_after();
+      if (cap.sink > 0.0f) l += cap.sink * exp2f(m_ref == -CUDART_INF_F ? 0.0f : -m_ref);
       const float inv = 1.0f / l;
       bf16* dst = out + ((size_t)(qs + tok_first + (valid ? tl : 0)) * nh + kvh * G + row % G) * hd;
 #pragma unroll
@@ -744,6 +746,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
     if (ok && nb > 0) ok = mbar_wait(o_done(w), 0, status, 13);
     if (ok) {
       tc_fence_after();
+      if (cap.sink > 0.0f) l += cap.sink * exp2f(m_ref == -CUDART_INF_F ? 0.0f : -m_ref);
       const float inv = 1.0f / l;
       bf16* dst = out + ((size_t)(qs + tok_first + (valid ? tl : 0)) * nh + kvh * G + row % G) * hd;
 #pragma unroll
@@ -888,14 +891,15 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
 }
 
 // As jb_attention_tc_prefill, with a chunked mask (chunk > 0: a query sees only the keys of its own chunk of
-// positions, counted from the sequence's first) and capped scores (softcap > 0: s -> softcap tanh(s / softcap)).
+// positions, counted from the sequence's first), capped scores (softcap > 0: s -> softcap tanh(s / softcap)) and a
+// sink (sink = 1: one more term exp(0) in the softmax's denominator).
 JB_EXPORT int jb_attention_tc_prefill_capped(const void* q, const void* k_cache, const void* v_cache, void* out,
                                              const int* block_table, const int* q_start, const int* kv_len, int T,
                                              int n_pages, int n_seqs, int max_q_len, int nh, int nkv, int hd,
                                              int page_size, int max_pages, int window, float scale, int chunk,
-                                             float softcap, int* status, cudaStream_t stream) {
+                                             float softcap, float sink, int* status, cudaStream_t stream) {
   JB_REFUSE(chunk < 0 || softcap < 0.0f || scale <= 0.0f, "attention_tc: a chunk, a cap and a scale cannot be negative");
-  const Cap cap = softcap > 0.0f ? Cap{chunk, softcap / scale, scale / softcap} : Cap{chunk, 0.0f, 0.0f};
+  const Cap cap = softcap > 0.0f ? Cap{chunk, softcap / scale, scale / softcap, sink} : Cap{chunk, 0.0f, 0.0f, sink};
   return tc_prefill_launch(q, k_cache, v_cache, out, block_table, q_start, kv_len, T, n_pages, n_seqs, max_q_len, nh,
                            nkv, hd, page_size, max_pages, window, scale, cap, status, stream);
 }

@@ -398,6 +398,31 @@ JB_EXPORT int jb_scale_softcap(float* x, long long n, float scale, float cap, cu
   return (int)cudaLaunchKernelEx(&cfg.c, scale_softcap_kernel, x, scale, cap, (size_t)n);
 }
 
+// x[t][:] *= sigmoid(gate[t * ld_gate]) in place: one gate a row (a shared expert's output gate, applied to the rows
+// that its last product reads; the product is linear, so the gate may stand before it).
+namespace {
+template <typename TX>
+__global__ void scale_rows_sigmoid_kernel(TX* __restrict__ x, const float* __restrict__ gate, int ld_gate, int N, size_t n) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float z = gate[(i / N) * ld_gate];
+    x[i] = jb::from_f32<TX>(jb::to_f32(x[i]) / (1.0f + expf(-z)));
+  }
+}
+}  // namespace
+
+JB_EXPORT int jb_scale_rows_sigmoid(void* x, int dtype, const float* gate, int ld_gate, int T, int N, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  const size_t n = (size_t)T * N;
+  jb::Launch cfg(dim3((unsigned)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192)), dim3(256), 0, stream);
+  if (dtype == JB_F32)
+    return (int)cudaLaunchKernelEx(&cfg.c, scale_rows_sigmoid_kernel<float>, (float*)x, gate, ld_gate, N, n);
+  if (dtype == JB_BF16)
+    return (int)cudaLaunchKernelEx(&cfg.c, scale_rows_sigmoid_kernel<bf16>, (bf16*)x, gate, ld_gate, N, n);
+  return JB_ERR_BAD_DTYPE;
+}
+
 // Rows of K bfloat16 copied into rows of Kp >= K with zeros behind them: the operand of a tensor-core product whose
 // width is no multiple of 8 (its weight is padded the same way when it is loaded).
 namespace {

@@ -3,7 +3,8 @@
 // sublayers made of two branches.  All arithmetic is float32.  For one row r of the stream (width W):
 //
 //   y  = ya                                                     (a sublayer's output), or, with branch weights,
-//   y  = mult (ya / rms(ya) wa + yb / rms(yb) wb)               rms(v) = sqrt(mean(v^2) + eps)
+//   y  = mult ya / rms(ya) wa + mult_b yb / rms(yb) wb          rms(v) = sqrt(mean(v^2) + eps), or, with two
+//   y  = mult ya + mult_b yb                                    branches and no branch weights, their weighted sum
 //   r <- r + scale * y          (scale per feature, or 1)       ya and yb are set to zero afterwards
 //   r <- r + extra              (another stream's row, e.g. the embedding's output that joins before a pass)
 //   x  = (r - mean(r)) / sqrt(mean((r - mean(r))^2) + eps) gamma        (center = 1: layer norm, no bias)
@@ -55,7 +56,7 @@ __device__ __forceinline__ void store_out(bf16* p, const Vec<4>& x) {
 template <typename TO, int V>
 __global__ void join_norm_kernel(float* __restrict__ stream, float* __restrict__ ya, float* __restrict__ yb,
                                  const float* __restrict__ wa, const float* __restrict__ wb, float mult,
-                                 const float* __restrict__ scale, const float* __restrict__ extra,
+                                 float mult_b, const float* __restrict__ scale, const float* __restrict__ extra,
                                  const float* __restrict__ gamma, float eps, int center, TO* __restrict__ x_out,
                                  const int* __restrict__ row_index, int W, float4* __restrict__ clear, size_t clear_n4,
                                  float4* __restrict__ clear2, size_t clear2_n4) {
@@ -70,9 +71,10 @@ __global__ void join_norm_kernel(float* __restrict__ stream, float* __restrict__
   float* pa = ya != nullptr ? ya + src * W : nullptr;
   float* pb = yb != nullptr ? yb + src * W : nullptr;
   const int first = threadIdx.x * V, step = blockDim.x * V;
-  const bool branches = pa != nullptr && wa != nullptr;
+  const bool branches = pa != nullptr && pb != nullptr;
+  const bool normed = branches && wa != nullptr;
   float inv_a = 1.0f, inv_b = 1.0f;
-  if (branches) {
+  if (normed) {
     float sa = 0.0f, sb = 0.0f;
     for (int i = first; i < W; i += step) {
       Vec<V> a, b;
@@ -104,10 +106,16 @@ __global__ void join_norm_kernel(float* __restrict__ stream, float* __restrict__
         Vec<V> b, ga, gb;
         b.load(pb + i);
         zero.store(pb + i);
-        ga.load(wa + i);
-        gb.load(wb + i);
+        if (normed) {
+          ga.load(wa + i);
+          gb.load(wb + i);
 #pragma unroll
-        for (int j = 0; j < V; ++j) y.v[j] = mult * ((y.v[j] * inv_a) * ga.v[j] + (b.v[j] * inv_b) * gb.v[j]);
+          for (int j = 0; j < V; ++j)
+            y.v[j] = mult * ((y.v[j] * inv_a) * ga.v[j]) + mult_b * ((b.v[j] * inv_b) * gb.v[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) y.v[j] = mult * y.v[j] + mult_b * b.v[j];
+        }
       }
       if (scale != nullptr) {
         Vec<V> sc;
@@ -157,11 +165,12 @@ __global__ void join_norm_kernel(float* __restrict__ stream, float* __restrict__
 }
 
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * act(gate[t, h, :]), one warp per (token, head);
-// weight [e] is shared by the heads; act: 0 = SiLU, 1 = sigmoid.
+// weight [e] is shared by the heads (w_stride 0) or every head has its own (w_stride e); act: 0 = SiLU, 1 = sigmoid.
+// With `denom` (float32 [T, heads]) o[t, h, :] is first divided by denom[t, h].
 template <typename TO>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate, int ld_gate,
-                                      const float* __restrict__ weight, float eps, int act, TO* __restrict__ out,
-                                      long long items, int heads, int e) {
+                                      const float* __restrict__ weight, int w_stride, const float* __restrict__ denom,
+                                      float eps, int act, TO* __restrict__ out, long long items, int heads, int e) {
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -170,14 +179,19 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
   const long long t = item / heads;
   const int h = (int)(item % heads);
   const float* row = o + (size_t)item * e;
+  const float under = denom != nullptr ? 1.0f / denom[item] : 1.0f;
   float ss = 0.0f;
-  for (int i = lane; i < e; i += 32) ss = fmaf(row[i], row[i], ss);
+  for (int i = lane; i < e; i += 32) {
+    const float v = row[i] * under;
+    ss = fmaf(v, v, ss);
+  }
   ss = jb::warp_sum(ss);
-  const float inv = 1.0f / sqrtf(ss / (float)e + eps);
+  const float inv = under / sqrtf(ss / (float)e + eps);
   const float* g = gate + (size_t)t * ld_gate + (size_t)h * e;
+  const float* w = weight + (size_t)h * w_stride;
   for (int i = lane; i < e; i += 32) {
     const float z = g[i], s = 1.0f / (1.0f + expf(-z));
-    out[(size_t)item * e + i] = jb::from_f32<TO>(((row[i] * inv) * weight[i]) * (act == 0 ? z * s : s));
+    out[(size_t)item * e + i] = jb::from_f32<TO>(((row[i] * inv) * w[i]) * (act == 0 ? z * s : s));
   }
 }
 
@@ -232,18 +246,20 @@ __global__ void sigmoid_gate_vec_kernel(TO* __restrict__ x, const float* __restr
 
 }  // namespace
 
-// stream: float32 [rows of the stream, W]; ya, yb: float32 of the stream's shape or null; wa, wb, scale, gamma: float32 [W]
+// stream: float32 [rows of the stream, W]; ya, yb: float32 of the stream's shape or null (yb without wa and wb: the
+// weighted sum mult ya + mult_b yb joins the stream); wa, wb, scale, gamma: float32 [W]
 // or null; extra: float32 of the stream's shape or null; x_out: [T, W] in out_dtype or null; row_index: int32 [T] or null.
 JB_EXPORT int jb_join_norm(float* stream, float* ya, float* yb, const float* wa, const float* wb, float mult,
-                           const float* scale, const float* extra, const float* gamma, float eps, int center,
+                           float mult_b, const float* scale, const float* extra, const float* gamma, float eps, int center,
                            void* x_out, int out_dtype, const int* row_index, int T, int W, float* clear,
                            long long clear_n, float* clear2, long long clear2_n, cudaStream_t stream_) {
   if (T <= 0) return 0;
   JB_REFUSE((clear != nullptr && ((clear_n & 3) != 0 || ((uintptr_t)clear & 15) != 0)) ||
                 (clear2 != nullptr && ((clear2_n & 3) != 0 || ((uintptr_t)clear2 & 15) != 0)),
             "join_norm: a buffer to clear is not made of whole 16-byte vectors");
-  JB_REFUSE((wa != nullptr) != (wb != nullptr) || (wa != nullptr && (ya == nullptr || yb == nullptr)),
-            "join_norm: two branches need two outputs and two weights");
+  JB_REFUSE((wa != nullptr) != (wb != nullptr) || (wa != nullptr && (ya == nullptr || yb == nullptr)) ||
+                (yb != nullptr && ya == nullptr),
+            "join_norm: two branches need two outputs, and two weights or none");
   JB_REFUSE(row_index != nullptr && (ya != nullptr || extra != nullptr), "join_norm: picked rows are only read");
   JB_REFUSE(x_out != nullptr && gamma == nullptr, "join_norm: a norm needs its weight");
   const size_t smem = (size_t)W * sizeof(float);
@@ -261,7 +277,7 @@ JB_EXPORT int jb_join_norm(float* stream, float* ya, float* yb, const float* wa,
       e = cudaFuncSetAttribute(join_norm_kernel<TO, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
       if (e != cudaSuccess) return (int)e;                                                                         \
     }                                                                                                              \
-    e = cudaLaunchKernelEx(&cfg.c, join_norm_kernel<TO, V>, stream, ya, yb, wa, wb, mult, scale, extra, gamma, eps, \
+    e = cudaLaunchKernelEx(&cfg.c, join_norm_kernel<TO, V>, stream, ya, yb, wa, wb, mult, mult_b, scale, extra, gamma, eps, \
                            center, (TO*)x_out, row_index, W, (float4*)clear, clear ? (size_t)clear_n >> 2 : (size_t)0, \
                            (float4*)clear2, clear2 ? (size_t)clear2_n >> 2 : (size_t)0);                           \
   } while (0)
@@ -275,17 +291,18 @@ JB_EXPORT int jb_join_norm(float* stream, float* ya, float* yb, const float* wa,
 }
 
 // o: float32 [T, heads e]; gate: float32 rows of ld_gate floats, head h at columns [h e, (h + 1) e); weight float32 [e].
-JB_EXPORT int jb_head_norm_gate(const float* o, const float* gate, int ld_gate, const float* weight, float eps, int act,
-                                void* out, int out_dtype, int T, int heads, int e, cudaStream_t stream) {
+JB_EXPORT int jb_head_norm_gate(const float* o, const float* gate, int ld_gate, const float* weight, int w_stride,
+                                const float* denom, float eps, int act, void* out, int out_dtype, int T, int heads,
+                                int e, cudaStream_t stream) {
   if (T <= 0) return 0;
   const long long items = (long long)T * heads;
   jb::Launch cfg(dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream);
   cudaError_t err;
   if (out_dtype == JB_F32)
-    err = cudaLaunchKernelEx(&cfg.c, head_norm_gate_kernel<float>, o, gate, ld_gate, weight, eps, act, (float*)out, items,
+    err = cudaLaunchKernelEx(&cfg.c, head_norm_gate_kernel<float>, o, gate, ld_gate, weight, w_stride, denom, eps, act, (float*)out, items,
                              heads, e);
   else if (out_dtype == JB_BF16)
-    err = cudaLaunchKernelEx(&cfg.c, head_norm_gate_kernel<bf16>, o, gate, ld_gate, weight, eps, act, (bf16*)out, items,
+    err = cudaLaunchKernelEx(&cfg.c, head_norm_gate_kernel<bf16>, o, gate, ld_gate, weight, w_stride, denom, eps, act, (bf16*)out, items,
                              heads, e);
   else
     return JB_ERR_BAD_DTYPE;

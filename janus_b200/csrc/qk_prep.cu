@@ -118,8 +118,10 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int ld, int Q
 // head_norm_rope_cache (grouped-query attention whose queries and keys are normed head by head):
 //   q = proj[:, 0 : H d], k = proj[:, H d : (H + G) d], v = proj[:, (H + G) d : (H + G) d + G e]
 //   every head of q and of k is divided by its own root mean square over d (eps inside the root) and multiplied by
-//   wq (or wk), a weight of size d that all heads share (null: no norm); then the first `rot` dimensions are turned
-//   as above.  q is written [T, H dp], k and v are appended to pages whose rows hold dp numbers (dp >= d, dp >= e; the
+//   wq (or wk), a weight of size d that all heads share (null: no norm, or with `unit` the division alone, which a
+//   rotation commutes with: it keeps every pair's sum of squares); then the first `rot` dimensions are turned as
+//   above, and q is multiplied by the query temperature 1 + temp_coef ln(floor((p + 1) / temp_every) + 1) of the
+//   token's position p (temp_every 0: none).  q is written [T, H dp], k and v are appended to pages whose rows hold dp numbers (dp >= d, dp >= e; the
 //   extra columns of q are zero, those of the pages are never written).  One block per token, a warp per head.
 template <typename TO>
 __global__ void head_norm_rope_cache_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ wq,
@@ -127,7 +129,7 @@ __global__ void head_norm_rope_cache_kernel(const float* __restrict__ proj, int 
                                             int rot, const int* __restrict__ positions, TO* __restrict__ q_out,
                                             const int* __restrict__ dest, TO* __restrict__ k_cache,
                                             TO* __restrict__ v_cache, int H, int G, int d, int e, int dp, int page_size,
-                                            int write_kv) {
+                                            int write_kv, int unit, float temp_coef, int temp_every) {
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   const int t = blockIdx.x;
@@ -142,6 +144,7 @@ __global__ void head_norm_rope_cache_kernel(const float* __restrict__ proj, int 
   const int half = rot >> 1;
   const float* cs = (table != nullptr && rot > 0) ? table + (size_t)positions[t] * half * 2 : nullptr;
   const int n_heads = H + (write_kv ? 2 * G : 0);
+  const float temp = temp_every > 0 ? 1.0f + temp_coef * logf((float)((positions[t] + 1) / temp_every) + 1.0f) : 1.0f;
   for (int head = warp; head < n_heads; head += warps) {
     if (head >= H + G) {                                // a value head: appended as projected
       const int g = head - H - G;
@@ -154,12 +157,13 @@ __global__ void head_norm_rope_cache_kernel(const float* __restrict__ proj, int 
     const float* x = pr + (size_t)head * d;
     const float* w = is_q ? wq : wk;
     float inv = 1.0f;
-    if (w != nullptr) {
+    if (w != nullptr || unit) {
       float ss = 0.0f;
       for (int j = lane; j < d; j += 32) ss = fmaf(x[j], x[j], ss);
       ss = jb::warp_sum(ss);
       inv = 1.0f / sqrtf(ss / (float)d + eps);
     }
+    if (is_q) inv *= temp;
     TO* out = is_q ? q_out + ((size_t)t * H + head) * dp
                    : k_cache + ((page * G + (head - H)) * page_size + prow) * dp;
     for (int j = lane; j < d; j += 32) {
@@ -232,11 +236,13 @@ JB_EXPORT int jb_latent_prep(const float* proj, int ld, int Q, int r, int rp, co
 }
 
 // proj: float32 [T, ld] = [q: H d | k: G d | v: G e]; wq, wk: float32 [d] or null; table: float32 [positions][rot/2][2]
-// or null; q_out [T, H dp] and the pages (rows of dp) in out_dtype.  write_kv = 0: q only.
+// or null; q_out [T, H dp] and the pages (rows of dp) in out_dtype.  write_kv = 0: q only.  unit = 1: heads are divided by
+// their root mean square also without a weight.  temp_every > 0: the query temperature.
 JB_EXPORT int jb_head_norm_rope_cache(const float* proj, int ld, const float* wq, const float* wk, float eps,
                                       const float* table, int rot, const int* positions, void* q_out, int out_dtype,
                                       const int* dest, void* k_cache, void* v_cache, int T, int H, int G, int d, int e,
-                                      int dp, int page_size, int write_kv, cudaStream_t stream) {
+                                      int dp, int page_size, int write_kv, int unit, float temp_coef, int temp_every,
+                                      cudaStream_t stream) {
   if (T <= 0) return 0;
   JB_REFUSE(dp < d || dp < e, "head_norm_rope_cache: heads of %d and %d cannot be stored in %d columns", d, e, dp);
   JB_REFUSE(rot < 0 || rot > d || (rot & 1), "head_norm_rope_cache: %d rotated dimensions do not fit a head of %d", rot, d);
@@ -246,10 +252,12 @@ JB_EXPORT int jb_head_norm_rope_cache(const float* proj, int ld, const float* wq
   cudaError_t err;
   if (out_dtype == JB_F32)
     err = cudaLaunchKernelEx(&cfg.c, head_norm_rope_cache_kernel<float>, proj, ld, wq, wk, eps, table, rot, positions,
-                             (float*)q_out, dest, (float*)k_cache, (float*)v_cache, H, G, d, e, dp, page_size, write_kv);
+                             (float*)q_out, dest, (float*)k_cache, (float*)v_cache, H, G, d, e, dp, page_size, write_kv,
+                             unit, temp_coef, temp_every);
   else if (out_dtype == JB_BF16)
     err = cudaLaunchKernelEx(&cfg.c, head_norm_rope_cache_kernel<bf16>, proj, ld, wq, wk, eps, table, rot, positions,
-                             (bf16*)q_out, dest, (bf16*)k_cache, (bf16*)v_cache, H, G, d, e, dp, page_size, write_kv);
+                             (bf16*)q_out, dest, (bf16*)k_cache, (bf16*)v_cache, H, G, d, e, dp, page_size, write_kv,
+                             unit, temp_coef, temp_every);
   else
     return JB_ERR_BAD_DTYPE;
   return (int)err;

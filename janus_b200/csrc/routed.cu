@@ -6,6 +6,8 @@
 //   scores s = sigmoid(z) of the router's float32 logits z [T, E]; a token's `top` experts are those with the largest
 //   scores (the lower index wins a tie); its weights are those scores, as they are.
 //   out[t] += sum over the chosen e of  Wd_e ( act(Wg_e x) * (Wu_e x) ),  x = s_e h[t]        (the weight is on the input)
+//   or, with the weight on the output,  out[t] += sum over the chosen e of  s_e Wd_e ( act(Wg_e h[t]) * (Wu_e h[t]) ).
+//   Scores may also be the softmax over all experts, and the choice may be limited to the best groups of neighbours.
 //
 // Experts' weights: gate and up [E][F][W], down [E][W][F], row-major, float32 or bfloat16.
 #include <math_constants.h>
@@ -18,22 +20,60 @@ namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int MAX_TOP = 16;
 
-// one warp per token
+// one warp per token.  softmax = 0: a score is the logit's sigmoid; 1: the softmax over all experts.  groups > 0: the
+// experts form `groups` equal groups of neighbours, a group's score is its largest score, and only experts of the
+// `keep` groups with the largest scores can be chosen (the lower group wins a tie).
 __global__ void route_topk_kernel(const float* __restrict__ logits, int ld, int E, int top, int* __restrict__ sel_e,
-                                  float* __restrict__ sel_w, int T) {
+                                  float* __restrict__ sel_w, int T, int softmax, int groups, int keep) {
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= T) return;
   const float* z = logits + (size_t)t * ld;
+  float z_max = 0.0f, z_sum = 1.0f;
+  if (softmax) {
+    z_max = -CUDART_INF_F;
+    for (int e = lane; e < E; e += 32) z_max = fmaxf(z_max, z[e]);
+    z_max = jb::warp_max(z_max);
+    z_sum = 0.0f;
+    for (int e = lane; e < E; e += 32) z_sum += expf(z[e] - z_max);
+    z_sum = jb::warp_sum(z_sum);
+  }
+  unsigned long long kept = ~0ull;               // bit g: experts of group g can be chosen
+  const int per_group = groups > 0 ? E / groups : E;
+  if (groups > 0) {
+    kept = 0ull;
+    for (int k = 0; k < keep; ++k) {
+      float best = -CUDART_INF_F;
+      int arg = 0x7fffffff;
+      for (int e = lane; e < E; e += 32) {
+        const int g = e / per_group;
+        const float v = z[e];                    // scores keep the order of the logits
+        if (!((kept >> g) & 1ull) && (v > best || (v == best && g < arg))) {
+          best = v;
+          arg = g;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) {
+          best = ob;
+          arg = oa;
+        }
+      }
+      if (arg < groups) kept |= 1ull << arg;
+    }
+  }
   int picked[MAX_TOP];
   for (int k = 0; k < top; ++k) {
     float best = -CUDART_INF_F;
     int arg = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
-      bool taken = false;
+      bool taken = groups > 0 && !((kept >> (e / per_group)) & 1ull);
       for (int q = 0; q < k; ++q) taken |= picked[q] == e;
-      const float v = z[e];            // the sigmoid keeps the order of the logits
+      const float v = z[e];            // the sigmoid and the softmax keep the order of the logits
       if (!taken && (v > best || (v == best && e < arg))) {
         best = v;
         arg = e;
@@ -51,7 +91,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int ld, int 
     picked[k] = arg;
     if (lane == 0) {
       sel_e[(size_t)t * top + k] = arg;
-      sel_w[(size_t)t * top + k] = 1.0f / (1.0f + expf(-best));
+      sel_w[(size_t)t * top + k] = softmax ? expf(best - z_max) / z_sum : 1.0f / (1.0f + expf(-best));
     }
   }
 }
@@ -111,7 +151,8 @@ __device__ __forceinline__ int pairs_of_expert(const int* __restrict__ sel_e, in
 template <typename TW, typename TX, bool VEC, int PB>
 __global__ void __launch_bounds__(GU_WARPS * 32) expert_gate_up_kernel(
     const TX* __restrict__ h, const int* __restrict__ sel_e, const float* __restrict__ sel_w, int top, int n_pairs,
-    const TW* __restrict__ w_gate, const TW* __restrict__ w_up, float* __restrict__ act, int W, int F, jb::Gate gate) {
+    const TW* __restrict__ w_gate, const TW* __restrict__ w_up, float* __restrict__ act, int W, int F, jb::Gate gate,
+    int weigh_input) {
   extern __shared__ __align__(16) float x_s[];           // [PB][W]
   __shared__ int list[GU_WARPS * 32];
   __shared__ int count;
@@ -128,7 +169,7 @@ __global__ void __launch_bounds__(GU_WARPS * 32) expert_gate_up_kernel(
       const int nb = min(PB, n - g0);
       for (int b = 0; b < nb; ++b) {
         const int pair = list[g0 + b];
-        const float s = sel_w[pair];
+        const float s = weigh_input ? sel_w[pair] : 1.0f;
         const TX* src = h + (size_t)(pair / top) * W;
         for (int i = threadIdx.x; i < W; i += blockDim.x) x_s[(size_t)b * W + i] = s * jb::to_f32(src[i]);
       }
@@ -198,11 +239,11 @@ __global__ void __launch_bounds__(GU_WARPS * 32) expert_gate_up_kernel(
 
 constexpr int DN_WARPS = 8, DN_ROWS = 4;
 
-// out[token of the pair][c] += Wd_e[c] . act[pair], a block per (rows, expert) as above
+// out[token of the pair][c] += Wd_e[c] . act[pair] (times out_w[pair] if given), a block per (rows, expert) as above
 template <typename TW, bool VEC, int PB>
 __global__ void __launch_bounds__(DN_WARPS * 32) expert_down_kernel(
-    const float* __restrict__ act, const int* __restrict__ sel_e, int top, int n_pairs, const TW* __restrict__ w_down,
-    float* __restrict__ out, int W, int F) {
+    const float* __restrict__ act, const int* __restrict__ sel_e, const float* __restrict__ out_w, int top, int n_pairs,
+    const TW* __restrict__ w_down, float* __restrict__ out, int W, int F) {
   extern __shared__ __align__(16) float a_s[];           // [PB][F]
   __shared__ int list[DN_WARPS * 32];
   __shared__ int count;
@@ -261,7 +302,8 @@ __global__ void __launch_bounds__(DN_WARPS * 32) expert_down_kernel(
 #pragma unroll
           for (int b = 0; b < PB; ++b) {
             if (b < nb) {
-              const float v = jb::warp_sum(acc[r][b]);
+              float v = jb::warp_sum(acc[r][b]);
+              if (out_w != nullptr) v *= out_w[list[g0 + b]];      // the pair's weight, on the expert's output
               if (lane == 0 && c0 + r < W) {
                 float* dst = out + (size_t)(list[g0 + b] / top) * W + c0 + r;
                 if (top == 1) *dst += v;                   // the token's only pair: nobody else adds here
@@ -324,7 +366,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) expert_plan_kernel(const int* __
   }
 }
 
-// rows[i] = weight[order[i]] * h[order[i] / top] in the products' dtype: the pairs (token, choice) in the order the
+// rows[i] = weight[order[i]] * h[order[i] / top] (no weights: the row itself) in the products' dtype: the pairs (token, choice) in the order the
 // experts' products take them
 template <typename TX>
 __global__ void expert_gather_kernel(const TX* __restrict__ h, const int* __restrict__ order,
@@ -332,7 +374,7 @@ __global__ void expert_gather_kernel(const TX* __restrict__ h, const int* __rest
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   const int pair = order[blockIdx.x];
-  const float s = sel_w[pair];
+  const float s = sel_w != nullptr ? sel_w[pair] : 1.0f;
   const TX* src = h + (size_t)(pair / top) * W;
   TX* dst = rows + (size_t)blockIdx.x * W;
   constexpr int N = Vec<TX>::N;
@@ -349,9 +391,9 @@ __global__ void expert_gather_kernel(const TX* __restrict__ h, const int* __rest
   for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = jb::from_f32<TX>(s * jb::to_f32(src[i]));
 }
 
-// out[t] += sum over k of results[where[t * top + k]]
-__global__ void expert_scatter_kernel(const float* __restrict__ results, const int* __restrict__ where, int top,
-                                      float* __restrict__ out, int W) {
+// out[t] += sum over k of results[where[t * top + k]] (times out_w[t * top + k] if given)
+__global__ void expert_scatter_kernel(const float* __restrict__ results, const int* __restrict__ where,
+                                      const float* __restrict__ out_w, int top, float* __restrict__ out, int W) {
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   const int t = blockIdx.x;
@@ -360,7 +402,8 @@ __global__ void expert_scatter_kernel(const float* __restrict__ results, const i
       float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       for (int k = 0; k < top; ++k) {
         const float4 r = *reinterpret_cast<const float4*>(results + (size_t)where[(size_t)t * top + k] * W + i);
-        v.x += r.x, v.y += r.y, v.z += r.z, v.w += r.w;
+        const float s = out_w != nullptr ? out_w[(size_t)t * top + k] : 1.0f;
+        v.x = fmaf(s, r.x, v.x), v.y = fmaf(s, r.y, v.y), v.z = fmaf(s, r.z, v.z), v.w = fmaf(s, r.w, v.w);
       }
       float4* o = reinterpret_cast<float4*>(out + (size_t)t * W + i);
       float4 a = *o;
@@ -371,7 +414,8 @@ __global__ void expert_scatter_kernel(const float* __restrict__ results, const i
   }
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float v = 0.0f;
-    for (int k = 0; k < top; ++k) v += results[(size_t)where[(size_t)t * top + k] * W + i];
+    for (int k = 0; k < top; ++k)
+      v = fmaf(out_w != nullptr ? out_w[(size_t)t * top + k] : 1.0f, results[(size_t)where[(size_t)t * top + k] * W + i], v);
     out[(size_t)t * W + i] += v;
   }
 }
@@ -379,20 +423,23 @@ __global__ void expert_scatter_kernel(const float* __restrict__ results, const i
 
 }  // namespace
 
-JB_EXPORT int jb_route_topk(const float* logits, int ld, int E, int top, int* sel_e, float* sel_w, int T,
-                            cudaStream_t stream) {
+JB_EXPORT int jb_route_topk(const float* logits, int ld, int E, int top, int* sel_e, float* sel_w, int T, int softmax,
+                            int groups, int keep, cudaStream_t stream) {
   if (T <= 0) return 0;
   JB_REFUSE(top < 1 || top > MAX_TOP || top > E, "route_topk: %d of %d experts (at most %d a token)", top, E, MAX_TOP);
+  JB_REFUSE(groups < 0 || groups > 64 || (groups > 0 && (E % groups != 0 || keep < 1 || keep > groups ||
+                                                          keep * (E / groups) < top)),
+            "route_topk: %d groups of which %d are kept do not fit %d experts and %d a token", groups, keep, E, top);
   jb::Launch cfg(dim3((T + 3) / 4), dim3(128), 0, stream);
-  return (int)cudaLaunchKernelEx(&cfg.c, route_topk_kernel, logits, ld, E, top, sel_e, sel_w, T);
+  return (int)cudaLaunchKernelEx(&cfg.c, route_topk_kernel, logits, ld, E, top, sel_e, sel_w, T, softmax, groups, keep);
 }
 
 // h: [T, W] in x_dtype; the experts' weights ([E] of them) in w_dtype; act: float32 scratch [T top, F]; out: float32
-// [T, W], added to.
+// [T, W], added to.  weight_on_output: a pair's weight multiplies its expert's output instead of its input.
 JB_EXPORT int jb_experts_few_tokens(const void* h, int x_dtype, const int* sel_e, const float* sel_w, int top,
                                     const void* w_gate, const void* w_up, const void* w_down, int w_dtype, float* act,
                                     float* out, int T, int W, int F, int E, float gate_limit, float gate_alpha,
-                                    cudaStream_t stream) {
+                                    int weight_on_output, cudaStream_t stream) {
   if (T <= 0) return 0;
   const int pairs = T * top;
   JB_REFUSE(E < 1 || E > 65535, "experts: %d experts", E);
@@ -410,14 +457,15 @@ JB_EXPORT int jb_experts_few_tokens(const void* h, int x_dtype, const int* sel_e
     if (smem1 > 48 * 1024) e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);      \
     if (e == cudaSuccess)                                                                                             \
       e = cudaLaunchKernelEx(&c1.c, k, (const TX*)h, sel_e, sel_w, top, pairs, (const TW*)w_gate, (const TW*)w_up,    \
-                             act, W, F, gate);                                                                        \
+                             act, W, F, gate, weight_on_output ? 0 : 1);                                              \
   } while (0)
 #define JB_LAUNCH_DN(TW, V, PB)                                                                                       \
   do {                                                                                                                \
     auto k = expert_down_kernel<TW, V, PB>;                                                                           \
     if (smem2 > 48 * 1024) e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);      \
     if (e == cudaSuccess)                                                                                             \
-      e = cudaLaunchKernelEx(&c2.c, k, (const float*)act, sel_e, top, pairs, (const TW*)w_down, out, W, F);           \
+      e = cudaLaunchKernelEx(&c2.c, k, (const float*)act, sel_e, weight_on_output ? sel_w : (const float*)nullptr,   \
+                             top, pairs, (const TW*)w_down, out, W, F);                                               \
   } while (0)
 #define JB_LAUNCH_EX(TW, TX)                                                                                          \
   do {                                                                                                                \
@@ -472,10 +520,11 @@ JB_EXPORT int jb_expert_gather(const void* h, int dtype, const int* order, const
   return (int)e;
 }
 
-// out[t] += sum_k results[where[t top + k]]; results float32 [pairs, W], out float32 [T, W]
-JB_EXPORT int jb_expert_scatter(const float* results, const int* where, int top, float* out, int T, int W,
-                                cudaStream_t stream) {
+// out[t] += sum_k out_w[t top + k] results[where[t top + k]] (out_w null: the plain sum); results float32 [pairs, W],
+// out float32 [T, W]
+JB_EXPORT int jb_expert_scatter(const float* results, const int* where, const float* out_w, int top, float* out, int T,
+                                int W, cudaStream_t stream) {
   if (T <= 0) return 0;
   jb::Launch cfg(dim3(T), dim3(W >= 1024 ? 256 : 128), 0, stream);
-  return (int)cudaLaunchKernelEx(&cfg.c, expert_scatter_kernel, results, where, top, out, W);
+  return (int)cudaLaunchKernelEx(&cfg.c, expert_scatter_kernel, results, where, out_w, top, out, W);
 }

@@ -56,20 +56,22 @@ _SIGNATURES = {
     "jb_embed_gather": "pippiippfp", "jb_rmsnorm": "pppifpiiiplp", "jb_residual_add": "ppilp",
     "jb_swiglu": "ppiiip", "jb_swiglu_f32_to_bf16": "piipiip", "jb_zero_f32": "plp",
     "jb_pack_weight_bf16": "piipp", "jb_rope_cache_write": "piipipppppiiiiiiip",
-    "jb_gemm_f32": "pppiiiiiip", "jb_attention_f32": "pppppppiiiiiiififp",
+    "jb_gemm_f32": "pppiiiiiip", "jb_attention_f32": "pppppppiiiiiiififfp",
     "jb_gemm_bf16": "pplipiiiiiiplpiffpp", "jb_gemm_bf16_pair": "pplipiiiiiiiffpp",
     "jb_gemm_bf16_pair_grouped": "pplipiiiiipiffpp", "jb_expert_plan": "piiiippppp",
     "jb_gemm_bf16_pair_qkv_rope": "ppliippppppiiiipp",
     "jb_sample": "piipfiffppupppp",
     "jb_attention_bf16_prefill": "pppppppiiiiiiiifp", "jb_attention_bf16_decode": "ppppppppiiiiiiifip",
     "jb_attention_bf16_decode_fused": "pipppppppppiiiiiiifiip",
-    "jb_attention_bf16_prefill_capped": "pppppppiiiiiiiififp", "jb_attention_bf16_decode_capped": "ppppppppiiiiiiifiifp",
-    "jb_join_norm": "pppppfpppfipipiiplplp", "jb_head_norm_gate": "ppipfipiiiip", "jb_sigmoid_gate": "pipiiiiip",
-    "jb_head_norm_rope_cache": "pippfpippipppiiiiiiiip",
+    "jb_attention_bf16_prefill_capped": "pppppppiiiiiiiififfp", "jb_attention_bf16_decode_capped": "ppppppppiiiiiiifiiffp",
+    "jb_join_norm": "pppppffpppfipipiiplplp", "jb_head_norm_gate": "ppipipfipiiiip", "jb_sigmoid_gate": "pipiiiiip",
+    "jb_head_norm_rope_cache": "pippfpippipppiiiiiiiiifip",
     "jb_delta_rule": "piiiipiiippfppllppiiiiip",
-    "jb_route_topk": "piiippip", "jb_experts_few_tokens": "pippipppippiiiiffp", "jb_expert_gather": "pippipiip",
-    "jb_expert_scatter": "ppipiip",
-    "jb_attention_tc_prefill": "pppppppiiiiiiiiiifpp", "jb_attention_tc_prefill_capped": "pppppppiiiiiiiiiififpp",
+    "jb_route_topk": "piiippiiiip", "jb_experts_few_tokens": "pippipppippiiiiffip", "jb_expert_gather": "pippipiip",
+    "jb_expert_scatter": "pppipiip",
+    "jb_gla_decay": "piiippfpiip", "jb_exp_gates": "piiippfppllppiip",
+    "jb_gated_linear_scan": "piiiifpiippplppiiiiiippp", "jb_scale_rows_sigmoid": "pipiiip",
+    "jb_attention_tc_prefill": "pppppppiiiiiiiiiifpp", "jb_attention_tc_prefill_capped": "pppppppiiiiiiiiiififfpp",
     "jb_streams_rmsnorm": "pppipifpiiipplp", "jb_streams_mix": "ppppiiip", "jb_streams_mix_rmsnorm": "pppppipifpiiiplp", "jb_embed_streams": "pippiiippp",
     "jb_lightning_scan": "piiiipppppiiiiiipp", "jb_gated_rmsnorm": "ppipifpiiip",
     "jb_conv_rope_cache": "pipipipppppippppiiiiiiip", "jb_conv_state_update": "pipippiip",
@@ -292,9 +294,10 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, accumulate: bool
 def attention_f32(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                   block_table: torch.Tensor, token_slot: torch.Tensor, positions: torch.Tensor,
                   nh: int, nkv: int, hd: int, page_size: int, window: int, scale: float, chunk: int = 0,
-                  softcap: float = 0.0) -> None:
+                  softcap: float = 0.0, sink: bool = False) -> None:
     """`chunk` > 0: a query sees only the keys of its own chunk of positions, [floor(pos / chunk) chunk, pos];
-    `softcap` > 0: a score s becomes softcap tanh(s / softcap)."""
+    `softcap` > 0: a score s becomes softcap tanh(s / softcap); `sink`: the softmax's denominator has one more
+    term, exp(0), a key of score 0 that has no value."""
     T = q.shape[0]
     _need(q, "attention q", torch.float32, (T, nh * hd))
     _need(out, "attention out", torch.float32, (T, nh * hd))
@@ -305,8 +308,8 @@ def attention_f32(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     _need(positions, "positions", torch.int32, (T,))
     _check(_lib("attention_f32").jb_attention_f32(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(token_slot), _ptr(positions),
-        T, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale, int(chunk), float(softcap), _stream()),
-        "attention_f32")
+        T, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale, int(chunk), float(softcap),
+        1.0 if sink else 0.0, _stream()), "attention_f32")
 
 
 # -- bfloat16 tensor-core matrix product --------------------------------------------
@@ -776,9 +779,10 @@ def _attention_lib(hd: int):
 def attention_bf16_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                            block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor,
                            n_seqs: int, max_q_len: int, nh: int, nkv: int, hd: int, page_size: int,
-                           window: int, scale: float, chunk: int = 0, softcap: float = 0.0) -> None:
+                           window: int, scale: float, chunk: int = 0, softcap: float = 0.0,
+                           sink: bool = False) -> None:
     """Causal attention of each sequence's new tokens (the last q_len positions of
-    its kv_len) over its cached keys.  `chunk`, `softcap`: as in `attention_f32`."""
+    its kv_len) over its cached keys.  `chunk`, `softcap`, `sink`: as in `attention_f32`."""
     T = q.shape[0]
     _need(q, "attention q", torch.bfloat16, (T, nh * hd))
     _need(out, "attention out", torch.bfloat16, (T, nh * hd))
@@ -787,11 +791,11 @@ def attention_bf16_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     _need(block_table, "block table", torch.int32)
     _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
     _need(kv_len, "kv_len", torch.int32, (n_seqs,))
-    if chunk or softcap:
+    if chunk or softcap or sink:
         _check(_attention_lib(hd).jb_attention_bf16_prefill_capped(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
             n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale, int(chunk),
-            float(softcap), _stream()), "attention_bf16_prefill")
+            float(softcap), 1.0 if sink else 0.0, _stream()), "attention_bf16_prefill")
         return
     _check(_attention_lib(hd).jb_attention_bf16_prefill(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
@@ -876,9 +880,9 @@ def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_ca
                           page_size: int, window: int, scale: float, workspace, max_kv_len: int,
                           n_splits: Optional[int] = None, qkv: Optional[torch.Tensor] = None,
                           cos_sin: Optional[torch.Tensor] = None, dest: Optional[torch.Tensor] = None,
-                          write_kv: bool = True, chunk: int = 0, softcap: float = 0.0) -> None:
-    """One new token per sequence (its last position) over its cached keys.  `chunk`, `softcap` (with `q` only): as
-    in `attention_f32`.
+                          write_kv: bool = True, chunk: int = 0, softcap: float = 0.0, sink: bool = False) -> None:
+    """One new token per sequence (its last position) over its cached keys.  `chunk`, `softcap`, `sink` (with `q`
+    only): as in `attention_f32`.
 
     Either `q` (rotated bf16 queries; the cache already holds the new token), or `qkv`: the
     projection's float32 output [B, (nh + 2 nkv) hd] (or [B, nh hd] with write_kv False), which the
@@ -900,19 +904,20 @@ def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_ca
     kernels = 2 if n_splits > 1 else 1
     if qkv is None:
         _need(q, "attention q", torch.bfloat16, (B, nh * hd))
-        if chunk or softcap:
+        if chunk or softcap or sink:
             _check(lib.jb_attention_bf16_decode_capped(
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(block_table),
                 _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale,
-                int(n_splits), int(chunk), float(softcap), _stream()), "attention_bf16_decode", kernels=kernels)
+                int(n_splits), int(chunk), float(softcap), 1.0 if sink else 0.0, _stream()),
+                "attention_bf16_decode", kernels=kernels)
             return
         _check(lib.jb_attention_bf16_decode(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(block_table),
             _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale,
             int(n_splits), _stream()), "attention_bf16_decode", kernels=kernels)
         return
-    if chunk or softcap:
-        raise KernelError("attention decode: the kernel that rotates and appends takes no chunked mask and no cap")
+    if chunk or softcap or sink:
+        raise KernelError("attention decode: the kernel that rotates and appends takes no chunked mask, cap or sink")
     _need(qkv, "qkv", torch.float32)
     width = (nh + 2 * nkv) * hd if write_kv else nh * hd
     if qkv.shape[0] != B or qkv.shape[1] < width:
@@ -947,8 +952,9 @@ def _attention_tc_row(hd: int) -> int:
 def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                          block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor,
                          n_seqs: int, max_q_len: int, nh: int, nkv: int, hd: int, page_size: int,
-                         window: int, scale: float, chunk: int = 0, softcap: float = 0.0) -> None:
-    """As attention_bf16_prefill, on the tcgen05 tensor cores.  `chunk`, `softcap`: as in `attention_f32`."""
+                         window: int, scale: float, chunk: int = 0, softcap: float = 0.0,
+                         sink: bool = False) -> None:
+    """As attention_bf16_prefill, on the tcgen05 tensor cores.  `chunk`, `softcap`, `sink`: as in `attention_f32`."""
     T = q.shape[0]
     _need(q, "attention q", torch.bfloat16, (T, nh * hd))
     _need(out, "attention out", torch.bfloat16, (T, nh * hd))
@@ -960,11 +966,12 @@ def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or k_cache.shape != v_cache.shape:
         raise KernelError(f"attention_tc: cache shape {tuple(k_cache.shape)} does not fit [pages, {nkv}, {page_size}, {hd}]")
     lib = _lib("attention_tc", _attention_tc_row(hd), lambda h: dict({"JB_HEAD_DIM": h}, **_ATTN_TC_DEFINES))
-    if chunk or softcap:
+    if chunk or softcap or sink:
         _check(lib.jb_attention_tc_prefill_capped(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
             T, k_cache.shape[0], n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window),
-            scale, int(chunk), float(softcap), _ptr(kernel_status(q.device)), _stream()), "attention_tc_prefill")
+            scale, int(chunk), float(softcap), 1.0 if sink else 0.0, _ptr(kernel_status(q.device)), _stream()),
+            "attention_tc_prefill")
         return
     _check(lib.jb_attention_tc_prefill(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
@@ -1422,12 +1429,13 @@ def gated_group_rmsnorm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tenso
 # -- layer norm, scaled sums into the residual stream, sublayers of two branches ---------------------------------
 def join_norm(stream: torch.Tensor, ya: Optional[torch.Tensor] = None, yb: Optional[torch.Tensor] = None,
               wa: Optional[torch.Tensor] = None, wb: Optional[torch.Tensor] = None, mult: float = 1.0,
-              scale: Optional[torch.Tensor] = None, extra: Optional[torch.Tensor] = None,
+              mult_b: Optional[float] = None, scale: Optional[torch.Tensor] = None, extra: Optional[torch.Tensor] = None,
               gamma: Optional[torch.Tensor] = None, eps: float = 0.0, center: bool = True,
               x_out: Optional[torch.Tensor] = None, row_index: Optional[torch.Tensor] = None,
               clear: Optional[torch.Tensor] = None, clear2: Optional[torch.Tensor] = None) -> None:
     """One launch, row by row of the float32 stream r [T, W], every step optional:
-    y = ya, or with branch weights y = mult (ya / rms(ya) wa + yb / rms(yb) wb); r += scale * y (ya, yb set to zero);
+    y = ya, or with branch weights y = mult ya / rms(ya) wa + mult_b yb / rms(yb) wb (mult_b None: mult), or with two
+    branches and no branch weights y = mult ya + mult_b yb; r += scale * y (ya, yb set to zero);
     r += extra; x_out = norm(r) * gamma (center: layer norm without bias, else root mean square), eps inside the
     roots.  With `row_index` x_out's rows are norm(r[row_index[i]]) and r is only read.  `clear`, `clear2`: float32
     scratch tensors (whole 16-byte vectors) set to zero on the way."""
@@ -1448,24 +1456,29 @@ def join_norm(stream: torch.Tensor, ya: Optional[torch.Tensor] = None, yb: Optio
         if c is not None:
             _need(c, "buffer to clear", torch.float32)
     _check(_lib("layer_norm").jb_join_norm(
-        _ptr(stream), _ptr(ya), _ptr(yb), _ptr(wa), _ptr(wb), float(mult), _ptr(scale), _ptr(extra), _ptr(gamma),
+        _ptr(stream), _ptr(ya), _ptr(yb), _ptr(wa), _ptr(wb), float(mult), float(mult if mult_b is None else mult_b),
+        _ptr(scale), _ptr(extra), _ptr(gamma),
         float(eps), int(bool(center)), _ptr(x_out), dtype_code(x_out.dtype) if x_out is not None else F32,
         _ptr(row_index), T, W, _ptr(clear), 0 if clear is None else clear.numel(), _ptr(clear2),
         0 if clear2 is None else clear2.numel(), _stream()), "join_norm")
 
 
 def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-                   heads: int, e: int, sigmoid: bool = False) -> None:
+                   heads: int, e: int, sigmoid: bool = False, denom: Optional[torch.Tensor] = None) -> None:
     """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * act(gate[t, h]) for float32 o [T, heads e], a float32
-    gate (a view whose rows may be wider) and a weight [e] that the heads share; act is SiLU, or the sigmoid."""
+    gate (a view whose rows may be wider) and a weight [e] that the heads share or [heads e] with a part for every
+    head; act is SiLU, or the sigmoid.  `denom` (float32 [T, heads]): o[t, h] is first divided by denom[t, h]."""
     T = o.shape[0]
     _need(o, "head outputs", torch.float32, (T, heads * e))
-    _need(weight, "head norm weight", torch.float32, (e,))
+    per_head = weight.numel() == heads * e and heads > 1
+    _need(weight, "head norm weight", torch.float32, (heads * e,) if per_head else (e,))
+    if denom is not None:
+        _need(denom, "divisors", torch.float32, (T, heads))
     _need(out, "gated heads", None, (T, heads * e))
     if gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape != o.shape:
         raise KernelError("head_norm_gate: the gate must be float32 columns of the heads' shape")
-    _check(_lib("layer_norm").jb_head_norm_gate(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), float(eps),
-                                                1 if sigmoid else 0, _ptr(out), dtype_code(out.dtype), T, heads, e,
+    _check(_lib("layer_norm").jb_head_norm_gate(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), e if per_head else 0,
+                                                _ptr(denom), float(eps), 1 if sigmoid else 0, _ptr(out), dtype_code(out.dtype), T, heads, e,
                                                 _stream()), "head_norm_gate")
 
 
@@ -1484,11 +1497,14 @@ def head_norm_rope_cache(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Opt
                          table: Optional[torch.Tensor], rot: int, positions: torch.Tensor, q_out: torch.Tensor,
                          dest: Optional[torch.Tensor], k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
                          heads: int, kv_heads: int, dim: int, vdim: int, stored_dim: int, page_size: int,
-                         write_kv: bool = True) -> None:
+                         write_kv: bool = True, unit_norm: bool = False, temp_coef: float = 0.0,
+                         temp_every: int = 0) -> None:
     """proj float32 [T, >= heads dim + kv_heads (dim + vdim)]: q, k and v as projected.  Every head of q and k is
     divided by its own root mean square and multiplied by the weight [dim] that the heads share (None: no norm), its
     first `rot` dimensions are turned by the table's cos and sin at the token's position; q is written
-    [T, heads stored_dim], k and v are appended to pages whose rows hold stored_dim numbers."""
+    [T, heads stored_dim], k and v are appended to pages whose rows hold stored_dim numbers.  `unit_norm`: without
+    weights the heads are still divided by their root mean square.  `temp_every` > 0: q is multiplied by
+    1 + temp_coef ln(floor((position + 1) / temp_every) + 1)."""
     T = q_out.shape[0]
     _need(proj, "projections", torch.float32)
     if proj.shape[0] != T:
@@ -1510,7 +1526,8 @@ def head_norm_rope_cache(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Opt
         _ptr(proj), proj.shape[1], _ptr(wq), _ptr(wk), float(eps), _ptr(table) if rot > 0 else None, int(rot),
         _ptr(positions), _ptr(q_out), dtype_code(q_out.dtype), _ptr(dest) if write_kv else None,
         _ptr(k_cache) if write_kv else None, _ptr(v_cache) if write_kv else None, T, heads, kv_heads, dim, vdim,
-        stored_dim, page_size, int(write_kv), _stream()), "head_norm_rope_cache")
+        stored_dim, page_size, int(write_kv), int(bool(unit_norm)), float(temp_coef), int(temp_every), _stream()),
+        "head_norm_rope_cache")
 
 
 # -- the gated delta rule ------------------------------------------------------------------------------------------
@@ -1540,21 +1557,28 @@ def delta_rule(conv: torch.Tensor, q_col: int, k_col: int, v_col: int, raw: torc
 
 
 # -- experts of which a token uses a few ---------------------------------------------------------------------------
-def route_topk(logits: torch.Tensor, top: int, sel_e: torch.Tensor, sel_w: torch.Tensor) -> None:
-    """Per row of the float32 logits [T, E]: the `top` largest (the lower index wins a tie) as indices (int32
-    [T, top]) and their sigmoids as weights (float32 [T, top])."""
-    T, E = logits.shape
+def route_topk(logits: torch.Tensor, top: int, sel_e: torch.Tensor, sel_w: torch.Tensor, softmax: bool = False,
+               groups: int = 0, keep: int = 0, experts: Optional[int] = None) -> None:
+    """Per row of the float32 logits [T, >= E] (the first `experts` columns; None: all): the `top` largest (the lower
+    index wins a tie) as indices (int32 [T, top]) and their scores as weights (float32 [T, top]): the logits' sigmoids,
+    or with `softmax` the softmax over all experts.  `groups` > 0: the experts form that many equal groups of
+    neighbours, and only experts of the `keep` groups whose best expert scores highest can be chosen."""
+    T, ld = logits.shape
+    E = ld if experts is None else int(experts)
     _need(logits, "router logits", torch.float32)
     _need(sel_e, "chosen experts", torch.int32, (T, top))
     _need(sel_w, "experts' weights", torch.float32, (T, top))
-    _check(_lib("routed").jb_route_topk(_ptr(logits), E, E, int(top), _ptr(sel_e), _ptr(sel_w), T, _stream()),
-           "route_topk")
+    if E > ld:
+        raise KernelError(f"route_topk: {E} experts in rows of {ld} logits")
+    _check(_lib("routed").jb_route_topk(_ptr(logits), ld, E, int(top), _ptr(sel_e), _ptr(sel_w), T,
+                                        int(bool(softmax)), int(groups), int(keep), _stream()), "route_topk")
 
 
 def experts_few_tokens(h: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, w_gate: torch.Tensor,
                        w_up: torch.Tensor, w_down: torch.Tensor, act: torch.Tensor, out: torch.Tensor,
-                       gate_limit: float = 0.0, gate_alpha: float = 1.0) -> None:
-    """out[t] += sum over the token's chosen experts e of Wd_e (act(Wg_e x) * (Wu_e x)) with x = weight * h[t]; an
+                       gate_limit: float = 0.0, gate_alpha: float = 1.0, weight_on_output: bool = False) -> None:
+    """out[t] += sum over the token's chosen experts e of Wd_e (act(Wg_e x) * (Wu_e x)) with x = weight * h[t] (or,
+    with `weight_on_output`, of weight * Wd_e (act(Wg_e h[t]) * (Wu_e h[t]))); an
     expert's rows are streamed once for up to four of the tokens that chose it (an expert nobody chose is not read),
     sums in float32.  w_gate, w_up [E, F, W], w_down
     [E, W, F] in h's dtype; act: float32 scratch [T top, F]; out float32 [T, W]."""
@@ -1571,8 +1595,8 @@ def experts_few_tokens(h: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor
     _need(out, "experts' out", torch.float32, (T, W))
     _check(_lib("routed").jb_experts_few_tokens(
         _ptr(h), dtype_code(h.dtype), _ptr(sel_e), _ptr(sel_w), top, _ptr(w_gate), _ptr(w_up), _ptr(w_down),
-        dtype_code(w_gate.dtype), _ptr(act), _ptr(out), T, W, F, E, float(gate_limit), float(gate_alpha), _stream()),
-        "experts_few_tokens", kernels=2)
+        dtype_code(w_gate.dtype), _ptr(act), _ptr(out), T, W, F, E, float(gate_limit), float(gate_alpha),
+        int(bool(weight_on_output)), _stream()), "experts_few_tokens", kernels=2)
 
 
 EXPERT_PLAN_MAX_EXPERTS = 1024
@@ -1596,23 +1620,119 @@ def expert_plan(sel_e: torch.Tensor, experts: int, F: int, W: int, order: torch.
                                          _ptr(gate_up_table), _ptr(down_table), _stream()), "expert_plan")
 
 
-def expert_gather(h: torch.Tensor, order: torch.Tensor, sel_w: torch.Tensor, top: int, rows: torch.Tensor) -> None:
-    """rows[i] = weight[order[i]] * h[order[i] // top]: the (token, choice) pairs in the order the experts' products
-    take them."""
+def expert_gather(h: torch.Tensor, order: torch.Tensor, sel_w: Optional[torch.Tensor], top: int,
+                  rows: torch.Tensor) -> None:
+    """rows[i] = weight[order[i]] * h[order[i] // top] (no weights: the rows themselves): the (token, choice) pairs in
+    the order the experts' products take them."""
     pairs, W = rows.shape
     _need(h, "expert input", rows.dtype)
     _need(rows, "gathered rows")
     _need(order, "pair order", torch.int32, (pairs,))
-    _need(sel_w, "experts' weights", torch.float32)
+    if sel_w is not None:
+        _need(sel_w, "experts' weights", torch.float32)
     _check(_lib("routed").jb_expert_gather(_ptr(h), dtype_code(h.dtype), _ptr(order), _ptr(sel_w), int(top), _ptr(rows),
                                            pairs, W, _stream()), "expert_gather")
 
 
-def expert_scatter(results: torch.Tensor, where: torch.Tensor, top: int, out: torch.Tensor) -> None:
-    """out[t] += sum_k results[where[t * top + k]] (float32)."""
+def expert_scatter(results: torch.Tensor, where: torch.Tensor, top: int, out: torch.Tensor,
+                   weights: Optional[torch.Tensor] = None) -> None:
+    """out[t] += sum_k weights[t, k] results[where[t * top + k]] (float32; no weights: the plain sum)."""
     T, W = out.shape
     _need(results, "experts' results", torch.float32)
     _need(where, "pair places", torch.int32, (T * top,))
     _need(out, "experts' out", torch.float32)
-    _check(_lib("routed").jb_expert_scatter(_ptr(results), _ptr(where), int(top), _ptr(out), T, W, _stream()),
-           "expert_scatter")
+    if weights is not None:
+        _need(weights, "experts' weights", torch.float32, (T, top))
+    _check(_lib("routed").jb_expert_scatter(_ptr(results), _ptr(where), _ptr(weights), int(top), _ptr(out), T, W,
+                                            _stream()), "expert_scatter")
+
+
+def scale_rows_sigmoid(x: torch.Tensor, gate: torch.Tensor) -> None:
+    """x[t] *= sigmoid(gate[t]) in place: one number per row, from a float32 column (a view with a row stride)."""
+    T, N = x.shape
+    _need(x, "rows to scale")
+    if gate.dtype != torch.float32 or gate.shape[0] != T or gate.dim() != 1:
+        raise KernelError("scale_rows_sigmoid: the gate must be a float32 column with one number per row")
+    _check(_lib("elementwise").jb_scale_rows_sigmoid(_ptr(x), dtype_code(x.dtype), _ptr(gate), gate.stride(0), T, N,
+                                                     _stream()), "scale_rows_sigmoid")
+
+
+# -- linear attention with gates that depend on the token --------------------------------------------------------
+GATED_LINEAR_SEGMENT = 128
+
+
+def gla_decay(proj: torch.Tensor, low_col: int, rank: int, a2t: torch.Tensor, bias: torch.Tensor, tau: float,
+              alpha: torch.Tensor) -> None:
+    """alpha[t, c] = sigmoid(z)^(1 / tau) with z = bias[c] + sum_j a2t[j, c] proj[t, low_col + j], in float32: the
+    decays per key channel of gated linear attention from the low-rank projection's output."""
+    T, C = alpha.shape
+    _need(proj, "projections", torch.float32)
+    _need(a2t, "second decay matrix, transposed", torch.float32, (rank, C))
+    _need(bias, "decay bias", torch.float32, (C,))
+    _need(alpha, "decays", torch.float32)
+    if proj.shape[0] != T or low_col + rank > proj.shape[1]:
+        raise KernelError("gla_decay: the projections do not hold the low-rank columns")
+    _check(_lib("gated_linear").jb_gla_decay(_ptr(proj), proj.shape[1], int(low_col), int(rank), _ptr(a2t), _ptr(bias),
+                                             1.0 / float(tau), _ptr(alpha), C, T, _stream()), "gla_decay")
+
+
+def exp_gates(proj: torch.Tensor, i_col: int, f_col: int, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float,
+              gates: torch.Tensor, state: torch.Tensor, m_off: int, q_start: torch.Tensor, seq_slot: torch.Tensor,
+              n_seqs: int, heads: int) -> None:
+    """Exponential gates with a running maximum per sequence and head: with i = cap tanh((zi + bi) / cap),
+    f = logsigmoid(cap tanh((zf + bf) / cap)) and m_t = max(f + m_(t-1), i), gates[t, h] = (exp(f + m_(t-1) - m_t),
+    exp(i - m_t), exp(-m_t), 0).  zi, zf are columns i_col + h, f_col + h of `proj`; m lives at state[slot, m_off + h]."""
+    T = proj.shape[0]
+    _need(proj, "projections", torch.float32)
+    _need(gates, "gates", torch.float32, (T, heads, 4))
+    _need(bias_i, "input gate bias", torch.float32, (heads,))
+    _need(bias_f, "forget gate bias", torch.float32, (heads,))
+    _need(state, "state", torch.float32)
+    _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
+    _need(seq_slot, "sequence slots", torch.int32, (n_seqs,))
+    if state.dim() != 2 or m_off + heads > state.shape[1] or max(i_col, f_col) + heads > proj.shape[1]:
+        raise KernelError("exp_gates: the state rows or the projections do not hold the gates' numbers")
+    _check(_lib("gated_linear").jb_exp_gates(_ptr(proj), proj.shape[1], int(i_col), int(f_col), _ptr(bias_i),
+                                             _ptr(bias_f), float(cap), _ptr(gates), _ptr(state), state.shape[1],
+                                             int(m_off), _ptr(q_start), _ptr(seq_slot), n_seqs, heads, _stream()),
+           "exp_gates")
+
+
+def gated_linear_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, q_scale: float, decays: torch.Tensor,
+                      out: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, seq_slot: torch.Tensor,
+                      n_seqs: int, heads: int, dim: int, vdim: int, max_q_len: int = 1, workspace=None,
+                      divisors: Optional[torch.Tensor] = None) -> None:
+    """Per sequence and head S <- diag(a_t) S + b_t k_t v_t^T, out_t = S^T (q_t q_scale) over the step's tokens in
+    order; proj float32 [T, ld] holds q, k, v at the given columns.  Without `divisors`, `decays` is float32
+    [T, heads dim], a decay per key channel, b = 1, and a slot's state row holds [heads, dim, vdim].  With `divisors`
+    (float32 [T, heads], written), `decays` is what `exp_gates` left ([T, heads, 4]: a_t and b_t one number a head),
+    a normalizer n <- a_t n + b_t k_t walks along, divisors[t, h] = max(|n . q|, exp(-m_t)) + 1e-6, and a slot's state
+    row holds per head [dim, vdim] then [dim] of n.  With a workspace, steps whose longest sequence brings more than
+    two segments of tokens run in passes over segments (4 launches); else one launch."""
+    T = proj.shape[0]
+    scalar = divisors is not None
+    _need(proj, "projections", torch.float32)
+    _need(out, "recurrence out", torch.float32, (T, heads * vdim))
+    _need(state, "state", torch.float32)
+    _need(decays, "decays", torch.float32, (T, heads, 4) if scalar else (T, heads * dim))
+    if scalar:
+        _need(divisors, "divisors", torch.float32, (T, heads))
+    per_head = dim * (vdim + (1 if scalar else 0))
+    if state.dim() != 2 or heads * per_head > state.shape[1]:
+        raise KernelError("gated_linear_scan: the state rows do not hold the recurrence's state")
+    _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
+    _need(seq_slot, "sequence slots", torch.int32, (n_seqs,))
+    if max(q_col + heads * dim, k_col + heads * dim, v_col + heads * vdim) > proj.shape[1]:
+        raise KernelError("gated_linear_scan: the projections' columns reach past the rows")
+    seg, scratch, seg_decay = 0, None, None
+    if workspace is not None and max_q_len > 2 * GATED_LINEAR_SEGMENT:
+        seg = GATED_LINEAR_SEGMENT
+        tiles = (max_q_len + seg - 1) // seg
+        scratch = workspace.get("gated_linear_segments", (n_seqs * tiles * heads * per_head,), torch.float32)
+        seg_decay = workspace.get("gated_linear_segment_decays", (n_seqs * tiles * heads * (1 if scalar else dim),),
+                                  torch.float32)
+    _check(_lib("gated_linear").jb_gated_linear_scan(
+        _ptr(proj), proj.shape[1], int(q_col), int(k_col), int(v_col), float(q_scale), _ptr(decays),
+        0 if scalar else heads * dim, int(scalar), _ptr(out), _ptr(divisors), _ptr(state), state.shape[1],
+        _ptr(q_start), _ptr(seq_slot), n_seqs, heads, dim, vdim, int(max_q_len), seg, _ptr(scratch), _ptr(seg_decay),
+        _stream()), "gated_linear_scan", kernels=4 if seg else 1)

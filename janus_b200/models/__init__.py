@@ -1,1 +1,1 @@
-from . import llama, mugedra, ramolix, zivitar  # noqa: F401  (registers LlamaForCausalLM, Mugedra, Ramolix and Zivitar)
+from . import buludra, llama, mugedra, ramolix, zivitar  # noqa: F401  (registers Buludra, LlamaForCausalLM, Mugedra, Ramolix and Zivitar)

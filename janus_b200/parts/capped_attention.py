@@ -8,6 +8,12 @@ turn the first `rotary_dims` dimensions of every head of q and k (pairing i with
 floor(i / chunk) = floor(j / chunk), chunks counted from the sequence's first position (chunk 0: every j <= i);
 ordinary softmax.  The concatenated heads are multiplied by sigmoid(Wg h) and projected by Wo.
 
+Options that other designs use: `qk_norm` "unit" divides the heads of q and k by their root mean square without a
+weight (after the rotation, which does not change a head's sum of squares, so the division is done on the way in);
+`q_temp` (coef, every) multiplies the query at position p by 1 + coef ln(floor((p + 1) / every) + 1), a temperature
+that grows with the sequence; `sink` adds one to the softmax's denominator, p_j = exp(s_j) / (1 + sum exp(s_j)): a key
+of score 0 that has no value, so a query may attend to nothing.
+
 q, k, v and the gate are one stacked product whose float32 accumulators one kernel turns into the queries and the
 cache rows (`ops.head_norm_rope_cache`); the attention itself is the library's grouped-query attention (tcgen05 for
 prompts, split keys for single tokens) with the cap and the chunk as arguments.  Keys and values share one stored head size, the larger of dim and vdim (the extra
@@ -27,8 +33,9 @@ from .linear import Linear
 
 class CappedAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
-                 eps: float, softcap: float = 0.0, chunk: int = 0, qk_norm: bool = True, gate: bool = True,
-                 position: Optional[PartSpec] = None, rotary_dims: int = 0,
+                 eps: float, softcap: float = 0.0, chunk: int = 0, qk_norm=True, gate: bool = True,
+                 position: Optional[PartSpec] = None, rotary_dims: int = 0, sink: bool = False,
+                 q_temp: Optional[tuple] = None,
                  dtype: torch.dtype = torch.bfloat16, device: torch.device = torch.device("cuda")):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} key/value heads")
@@ -39,7 +46,13 @@ class CappedAttention(Mixer):
         self.hidden_size, self.nh, self.nkv = int(hidden_size), int(num_heads), int(num_kv_heads)
         self.dim, self.vdim = int(dim), int(vdim)
         self.scale, self.eps, self.softcap, self.chunk = float(scale), float(eps), float(softcap), int(chunk)
-        self.qk_norm, self.gate = bool(qk_norm), bool(gate)
+        if qk_norm not in (True, False, "unit"):
+            raise ValueError(f"qk_norm is True (with weights), False or 'unit' (without), got {qk_norm!r}")
+        self.unit_norm = qk_norm == "unit"
+        self.qk_norm, self.gate, self.sink = qk_norm is True, bool(gate), bool(sink)
+        self.temp_coef, self.temp_every = (0.0, 0) if q_temp is None else (float(q_temp[0]), int(q_temp[1]))
+        if self.temp_every < 0:
+            raise ValueError(f"a query temperature steps every {self.temp_every} positions")
         self.dtype, self.device = dtype, device
         self.stored = stored_head_size(max(self.dim, self.vdim), dtype)
         _check_kernel_limits(self.nh, self.nkv, self.stored, dtype)
@@ -108,24 +121,25 @@ class CappedAttention(Mixer):
         q = ws.get("capped_q", (T, self.nh * D), self.dtype)
         ops.head_norm_rope_cache(proj, self.wq, self.wk, self.eps, table, self.rotary_dims, ctx.positions, q,
                                  group.dest_rows, cache_view.k, cache_view.v, self.nh, self.nkv, self.dim, self.vdim, D,
-                                 group.page_size)
+                                 group.page_size, unit_norm=self.unit_norm, temp_coef=self.temp_coef,
+                                 temp_every=self.temp_every)
         attn = ws.get("capped_attn", (T, self.nh * D), self.dtype)
         if self.dtype == torch.float32:
             ops.attention_f32(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.token_seq, ctx.positions,
-                              self.nh, self.nkv, D, group.page_size, 0, self.scale, self.chunk, self.softcap)
+                              self.nh, self.nkv, D, group.page_size, 0, self.scale, self.chunk, self.softcap, sink=self.sink)
         elif ctx.is_decode:
             ops.attention_bf16_decode(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.kv_len, self.nh,
                                       self.nkv, D, group.page_size, 0, self.scale, ctx.workspace,
                                       min(ctx.max_kv_len_bound, self.chunk) if self.chunk else ctx.max_kv_len_bound,
-                                      chunk=self.chunk, softcap=self.softcap)
+                                      chunk=self.chunk, softcap=self.softcap, sink=self.sink)
         elif ops.attention_tc_supported(self.nh, self.nkv, D):
             ops.attention_tc_prefill(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.q_start, ctx.kv_len,
                                      ctx.n_seqs, ctx.max_q_len, self.nh, self.nkv, D, group.page_size, 0, self.scale,
-                                     self.chunk, self.softcap)
+                                     self.chunk, self.softcap, sink=self.sink)
         else:
             ops.attention_bf16_prefill(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.q_start, ctx.kv_len,
                                        ctx.n_seqs, ctx.max_q_len, self.nh, self.nkv, D, group.page_size, 0, self.scale,
-                                       self.chunk, self.softcap)
+                                       self.chunk, self.softcap, sink=self.sink)
         if self.gate:
             ops.sigmoid_gate(attn, proj[:, self.gate_col:], self.nh, self.vdim, D)
         self.o.forward_add(attn, residual)

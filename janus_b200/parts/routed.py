@@ -14,6 +14,14 @@ order of the token's choices.  Where the sizes allow it (width and inner width m
 (`ops.expert_plan`), and each of the two products is ONE launch over the stack of all experts' matrices whose tiles
 that kernel listed (`ops.gemm_bf16_grouped`): the host never reads the choice.  Other sizes read the choice back
 and launch each expert's products by themselves.  The float32 engine always streams.
+
+Options that other designs use.  `score` "softmax": the scores are the softmax of the logits over all experts (still
+taken as they are).  `groups` (count, keep): the experts form `count` equal groups of neighbours, a group's score is
+its largest score, and only experts of the `keep` best groups can be chosen.  `weight_on` "output": the weight
+multiplies the expert's output, out = sum over the chosen e of s_e expert_e(h).  `shared_size`: one more gated
+feed-forward of that inner width runs for every token and is added; with `shared_gate` it is multiplied by
+sigmoid(wsg . h), one number per token (the gate's row rides along in the router's product, and because the last
+product is linear the gate multiplies the rows that product reads).
 """
 from __future__ import annotations
 
@@ -31,16 +39,36 @@ MAX_STREAM_PAIRS = 65535  # pairs of one launch of the streaming kernels
 
 
 class RoutedExperts(FeedForward):
-    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int,
+    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, score: str = "sigmoid",
+                 groups: Optional[tuple] = None, weight_on: str = "input", shared_size: Optional[int] = None,
+                 shared_gate: bool = False,
                  dtype: torch.dtype = torch.bfloat16, device: torch.device = torch.device("cuda")):
         if not 1 <= top <= experts:
             raise ValueError(f"a token uses {top} of {experts} experts")
+        if score not in ("sigmoid", "softmax") or weight_on not in ("input", "output"):
+            raise ValueError(f"scores are 'sigmoid' or 'softmax' and weigh the 'input' or the 'output', got "
+                             f"{score!r}, {weight_on!r}")
+        self.softmax, self.weight_on_output = score == "softmax", weight_on == "output"
+        self.groups, self.keep = (0, 0) if groups is None else (int(groups[0]), int(groups[1]))
+        if groups is not None and (self.groups < 1 or self.groups > 64 or experts % self.groups
+                                   or not 1 <= self.keep <= self.groups or self.keep * (experts // self.groups) < top):
+            raise ValueError(f"{self.groups} groups of which {self.keep} are kept do not fit {experts} experts "
+                             f"and {top} a token")
+        self.shared_size = None if shared_size is None else int(shared_size)
+        self.shared_gate = bool(shared_gate) and self.shared_size is not None
         if top > 16:
             raise ValueError(f"at most 16 experts a token are supported, got {top}")
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.experts, self.top = int(experts), int(top)
         self.dtype, self.device = dtype, device
-        self.router = Linear(hidden_size, experts, dtype, device, name="router", pad_width=True)
+        # the router's product also makes the shared expert's gate: one more row
+        self.router = Linear(hidden_size, experts + (1 if self.shared_gate else 0), dtype, device, name="router",
+                             pad_width=True)
+        self.shared_gate_up = self.shared_down = None
+        if self.shared_size is not None:
+            self.shared_gate_up = GatedLinear(hidden_size, self.shared_size, dtype, device, name="shared_gate_up",
+                                              pad_width=True)
+            self.shared_down = Linear(self.shared_size, hidden_size, dtype, device, name="shared_down", pad_width=True)
         self.w_gate = self.w_up = self.w_down = None           # [E, F, W], [E, F, W], [E, W, F] row-major
         self.gate_up: List[GatedLinear] = []                   # bfloat16 engine: the experts' tensor-core products
         self.down: List[Linear] = []
@@ -55,10 +83,20 @@ class RoutedExperts(FeedForward):
         for e in range(self.experts):
             shapes.update({f"e{e}_gate": ((F, W), "normal"), f"e{e}_up": ((F, W), "normal"),
                            f"e{e}_down": ((W, F), "normal")})
+        if self.shared_size is not None:
+            shapes.update({"shared_gate": ((self.shared_size, W), "normal"), "shared_up": ((self.shared_size, W), "normal"),
+                           "shared_down": ((W, self.shared_size), "normal")})
+            if self.shared_gate:
+                shapes["shared_sg"] = ((1, W), "normal")
         return shapes
 
-    def load(self, router: torch.Tensor, **experts: torch.Tensor) -> None:
-        self.router.load([router])
+    def load(self, router: torch.Tensor, shared_gate: Optional[torch.Tensor] = None,
+             shared_up: Optional[torch.Tensor] = None, shared_down: Optional[torch.Tensor] = None,
+             shared_sg: Optional[torch.Tensor] = None, **experts: torch.Tensor) -> None:
+        self.router.load([router] + ([shared_sg] if self.shared_gate else []))
+        if self.shared_size is not None:
+            self.shared_gate_up.load(shared_gate, shared_up)
+            self.shared_down.load([shared_down])
         W, F, E = self.hidden_size, self.intermediate_size, self.experts
 
         def stack(kind: str, shape) -> torch.Tensor:
@@ -85,11 +123,18 @@ class RoutedExperts(FeedForward):
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         T = x.shape[0]
         ws = ctx.workspace
-        logits = ws.get("router_logits", (T, self.experts), torch.float32)
+        logits = ws.get("router_logits", (T, self.router.out_features), torch.float32)
         self.router.forward(x, logits)
+        if self.shared_size is not None:
+            shared = ws.get("shared_act", (T, self.shared_size), self.dtype)
+            self.shared_gate_up.forward(x, shared, ctx)
+            if self.shared_gate:
+                ops.scale_rows_sigmoid(shared, logits[:, self.experts])
+            self.shared_down.forward_add(shared, residual)
         sel_e = ws.get("router_experts", (T, self.top), torch.int32)
         sel_w = ws.get("router_weights", (T, self.top), torch.float32)
-        ops.route_topk(logits, self.top, sel_e, sel_w)
+        ops.route_topk(logits, self.top, sel_e, sel_w, softmax=self.softmax, groups=self.groups, keep=self.keep,
+                       experts=self.experts)
         pairs = T * self.top
         if self.dtype == torch.bfloat16 and not ctx.is_decode and pairs > FEW_PAIRS:
             if self.grouped:
@@ -102,7 +147,8 @@ class RoutedExperts(FeedForward):
         for t0 in range(0, T, rows):
             t1 = min(T, t0 + rows)
             ops.experts_few_tokens(x[t0:t1], sel_e[t0:t1], sel_w[t0:t1], self.w_gate, self.w_up, self.w_down,
-                                   act[t0 * self.top: t1 * self.top], residual[t0:t1])
+                                   act[t0 * self.top: t1 * self.top], residual[t0:t1],
+                                   weight_on_output=self.weight_on_output)
 
     def _grouped(self, x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         """The tensor-core path of a prompt step without the host: sort, gather, two grouped products, add back."""
@@ -116,12 +162,12 @@ class RoutedExperts(FeedForward):
         table_dn = ws.get("experts_down_tiles", (4 + 4 * max_dn,), torch.int32)
         ops.expert_plan(sel_e, E, F, W, index[0], index[1], table_gu, table_dn)
         rows = ws.get("experts_rows", (pairs, W), self.dtype)
-        ops.expert_gather(x, index[0], sel_w, top, rows)
+        ops.expert_gather(x, index[0], None if self.weight_on_output else sel_w, top, rows)
         act = ws.get("experts_act_rows", (pairs, F), self.dtype)
         ops.gemm_bf16_grouped(rows, self.gate_up_stack, act, table_gu, max_gu, mode="swiglu", label="expert_gate_up")
         results = ws.get("experts_results", (pairs, W), torch.float32)
         ops.gemm_bf16_grouped(act, self.down_stack, results, table_dn, max_dn, mode="store", label="expert_down")
-        ops.expert_scatter(results, index[1], top, residual)
+        ops.expert_scatter(results, index[1], top, residual, weights=sel_w if self.weight_on_output else None)
 
     def _by_expert(self, x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         """The tensor-core path of a prompt step: the host reads the choice, sorts the (token, choice) pairs by expert
@@ -136,7 +182,7 @@ class RoutedExperts(FeedForward):
         index = torch.from_numpy(np.concatenate([order, where])).to(self.device)
         ws = ctx.workspace
         rows = ws.get("experts_rows", (pairs, W), self.dtype)
-        ops.expert_gather(x, index[:pairs], sel_w, top, rows)
+        ops.expert_gather(x, index[:pairs], None if self.weight_on_output else sel_w, top, rows)
         act = ws.get("experts_act_rows", (pairs, F), self.dtype)
         results = ws.get("experts_results", (pairs, W), torch.float32)
         start = 0
@@ -146,7 +192,7 @@ class RoutedExperts(FeedForward):
                 self.gate_up[e].forward(rows[start:start + n], act[start:start + n], ctx)
                 self.down[e].forward(act[start:start + n], results[start:start + n])
                 start += n
-        ops.expert_scatter(results, index[pairs:], top, residual)
+        ops.expert_scatter(results, index[pairs:], top, residual, weights=sel_w if self.weight_on_output else None)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)
