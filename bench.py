@@ -21,7 +21,7 @@ the same weights (`checked`).
 
 Other modes (one JSON line per item, none of them the headline): --kernels,
 --prompt-lengths, --workload 1b|13b, --deterministic, --plan-check, --cpu-baseline, --float32, --design
-(the Zivitar design, or with --design-model ramolix | mugedra another one, beside the Llama decoder at equal layer
+(the Zivitar design, or with --design-model ramolix | mugedra | buludra another one, beside the Llama decoder at equal layer
 sizes: prompt and decode throughput, a step's kernels).
 """
 import argparse
@@ -701,14 +701,37 @@ def mugedra_config(width, ff, heads, kv_heads, window, vocab):
                 layers=[layer, layer, layer])
 
 
-DESIGNS = {"zivitar": zivitar_config, "ramolix": ramolix_config, "mugedra": mugedra_config}
+def buludra_config(width, ff, heads, kv_heads, window, vocab):
+    """Four layers at the size's width: sink attention (head size 128, half of it rotated) beside a matrix memory with
+    exponential gates (as many heads of 128 by 128 state) with a dense feed-forward; attention with normed heads and a
+    query temperature with experts; gated linear attention (as many heads of 128 by 128 state, decays of rank 64)
+    with a dense feed-forward; the two mixers side by side again with experts.  Eight experts of half the size's
+    feed-forward each in four groups of which two are kept, two experts a token (the dense feed-forward's products
+    per token), and a shared expert of a quarter of it."""
+    side = dict(left=dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=0.5 * 128 ** -0.5,
+                          rot=dict(dims=64, base=10000.0)),
+                right=dict(heads=heads, dim=128, vdim=128, gate_cap=15.0), left_scale=0.8, right_scale=0.9)
+    experts = dict(kind="moe", expert=dict(ff=ff // 2), router=dict(experts=8, top=2, groups=dict(count=4, keep=2)),
+                   shared=dict(ff=ff // 4))
+    dense = dict(kind="dense", ff=ff)
+    return dict(architecture="Buludra", vocab=vocab, width=width, norm=dict(eps=1e-5), logit_softcap=30.0,
+                layers=[dict(type="parallel", mixer=side, mlp=dense),
+                        dict(type="attention", mlp=experts,
+                             mixer=dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5,
+                                        q_temp=dict(coef=0.1, every=1024))),
+                        dict(type="gla", mlp=dense, mixer=dict(heads=heads, dim=128, vdim=128, tau=16.0, rank=64)),
+                        dict(type="parallel", mixer=side, mlp=experts)])
+
+
+DESIGNS = {"zivitar": zivitar_config, "ramolix": ramolix_config, "mugedra": mugedra_config, "buludra": buludra_config}
 # what a design is measured beside: the Llama decoder, or the design whose kernels are most like its own
-BESIDE = {"zivitar": ("llama",), "ramolix": ("llama",), "mugedra": ("ramolix", "llama")}
+BESIDE = {"zivitar": ("llama",), "ramolix": ("llama",), "mugedra": ("ramolix", "llama"), "buludra": ("mugedra", "llama")}
 
 
 def run_design(which, design="zivitar"):
-    """A design (Zivitar, Ramolix or Mugedra) beside the Llama decoder, and Mugedra also beside Ramolix, whose
-    mixers (a recurrence behind a short convolution, attention over part of the keys) are most like its own, at equal
+    """A design (Zivitar, Ramolix, Mugedra or Buludra) beside the Llama decoder, Mugedra also beside Ramolix, whose
+    mixers (a recurrence behind a short convolution, attention over part of the keys) are most like its own, and
+    Buludra also beside Mugedra (two mixers side by side, a recurrence with a matrix state, experts), at equal
     layer sizes (random weights, four layer runs):
     prompt steps and decode steps timed on the device, and each step's kernels one by one (`Model.profile`).  One
     JSON line per (size, model)."""

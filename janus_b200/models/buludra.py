@@ -62,7 +62,7 @@ def _mixer_spec(config: BuludraConfig, i: int) -> PartSpec:
 def _feed_forward_spec(config: BuludraConfig, i: int) -> PartSpec:
     mlp, p = config.layers[i].mlp, f"l{i}.mlp."
     if isinstance(mlp, DenseConfig):
-        return PartSpec("swiglu", dict(hidden_size=config.width, intermediate_size=mlp.ff),
+        return PartSpec("swiglu", dict(hidden_size=config.width, intermediate_size=mlp.ff, pad_width=True),
                         weights=dict(gate=p + "gate", up=p + "up", down=p + "down"))
     weights = {"router": p + "router"}
     for e in range(mlp.experts):

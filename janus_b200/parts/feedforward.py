@@ -10,12 +10,14 @@ from .linear import GatedLinear, Linear
 
 
 class SwiGLUFeedForward(FeedForward):
-    def __init__(self, hidden_size: int, intermediate_size: int,
+    """`pad_width`: widths that are no multiple of 8 run on zero-padded operands in bfloat16 instead of being refused."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, pad_width: bool = False,
                  dtype: torch.dtype = torch.bfloat16, device: torch.device = torch.device("cuda")):
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.dtype, self.device = dtype, device
-        self.gate_up = GatedLinear(hidden_size, intermediate_size, dtype, device)
-        self.down = Linear(intermediate_size, hidden_size, dtype, device, name="down")
+        self.gate_up = GatedLinear(hidden_size, intermediate_size, dtype, device, pad_width=pad_width)
+        self.down = Linear(intermediate_size, hidden_size, dtype, device, name="down", pad_width=pad_width)
 
     def weight_shapes(self):
         return {"gate": ((self.intermediate_size, self.hidden_size), "normal"),

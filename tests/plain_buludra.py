@@ -133,19 +133,30 @@ def sink_attention(p: dict, w: Dict[str, torch.Tensor], pre: str, h: torch.Tenso
 # ---------------------------------------------------------------------------------------------
 # gated linear attention: a decay per key channel
 # ---------------------------------------------------------------------------------------------
+def decay_recurrence(q, k, v, alpha, S: Optional[torch.Tensor] = None):
+    """q, k, alpha [T, H, d], v [T, H, e]: S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t; returns (o, S)."""
+    T, H, d, e = q.shape[0], q.shape[1], q.shape[2], v.shape[2]
+    S = torch.zeros(H, d, e, dtype=DT) if S is None else S.clone()
+    o = torch.zeros(T, H, e, dtype=DT)
+    for t in range(T):
+        S = alpha[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        o[t] = torch.einsum("hde,hd->he", S, q[t])
+    return o, S
+
+
+def channel_decays(low: torch.Tensor, a2: torch.Tensor, bias: torch.Tensor, tau: float) -> torch.Tensor:
+    """sigmoid(z)^(1/tau) with z = A2 low + bias."""
+    return torch.exp(log_sigmoid(low @ a2.T + bias) / tau)
+
+
 def gated_linear_attention(p: dict, w: Dict[str, torch.Tensor], pre: str, h: torch.Tensor, eps: float,
                            state: Optional[dict]):
     T, H, d, e = h.shape[0], p["heads"], p["dim"], p["vdim"]
     q = (h @ w[pre + "q"].T).view(T, H, d) * d ** -0.5
     k = (h @ w[pre + "k"].T).view(T, H, d)
     v = (h @ w[pre + "v"].T).view(T, H, e)
-    z = (h @ w[pre + "a1"].T) @ w[pre + "a2"].T + w[pre + "a2.b"]
-    alpha = torch.exp(log_sigmoid(z) / p["tau"]).view(T, H, d)
-    S = torch.zeros(H, d, e, dtype=DT) if state is None else state["S"].clone()
-    o = torch.zeros(T, H, e, dtype=DT)
-    for t in range(T):
-        S = alpha[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hde,hd->he", S, q[t])
+    alpha = channel_decays(h @ w[pre + "a1"].T, w[pre + "a2"], w[pre + "a2.b"], p["tau"]).view(T, H, d)
+    o, S = decay_recurrence(q, k, v, alpha, None if state is None else state["S"])
     o = rms_unit(o, eps) * w[pre + "norm"]
     y = o.reshape(T, H * e) * silu(h @ w[pre + "g"].T)
     return y @ w[pre + "o"].T, {"S": S}
@@ -154,13 +165,16 @@ def gated_linear_attention(p: dict, w: Dict[str, torch.Tensor], pre: str, h: tor
 # ---------------------------------------------------------------------------------------------
 # matrix memory with exponential gates and a running maximum
 # ---------------------------------------------------------------------------------------------
-def matrix_memory(p: dict, w: Dict[str, torch.Tensor], pre: str, h: torch.Tensor, eps: float, state: Optional[dict]):
-    T, H, d, e, cap = h.shape[0], p["heads"], p["dim"], p["vdim"], p["gate_cap"]
-    q = (h @ w[pre + "q"].T).view(T, H, d) * d ** -0.5
-    k = (h @ w[pre + "k"].T).view(T, H, d)
-    v = (h @ w[pre + "v"].T).view(T, H, e)
-    gi = cap * torch.tanh((h @ w[pre + "i"].T + w[pre + "i.b"]) / cap)                    # [T, H], a logarithm
-    gf = log_sigmoid(cap * torch.tanh((h @ w[pre + "f"].T + w[pre + "f.b"]) / cap))       # [T, H], a logarithm
+def log_gates(zi, zf, bias_i, bias_f, cap: float):
+    """The logarithms of the input and the forget gate: cap tanh((zi + bi) / cap), logsigmoid(cap tanh((zf + bf) / cap))."""
+    return cap * torch.tanh((zi + bias_i) / cap), log_sigmoid(cap * torch.tanh((zf + bias_f) / cap))
+
+
+def exp_gate_recurrence(q, k, v, gi, gf, state: Optional[dict] = None):
+    """q, k [T, H, d], v [T, H, e], log gates gi, gf [T, H].  With the running maximum m (0 at the start):
+    m_t = max(gf + m, gi); S_t = exp(gf + m - m_t) S + exp(gi - m_t) k v^T; n likewise with k alone;
+    o_t = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6).  Returns (o, state)."""
+    T, H, d, e = q.shape[0], q.shape[1], q.shape[2], v.shape[2]
     if state is None:
         S, n, m = torch.zeros(H, d, e, dtype=DT), torch.zeros(H, d, dtype=DT), torch.zeros(H, dtype=DT)
     else:
@@ -174,8 +188,18 @@ def matrix_memory(p: dict, w: Dict[str, torch.Tensor], pre: str, h: torch.Tensor
         m = m_new
         below = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-m)) + 1e-6
         o[t] = torch.einsum("hde,hd->he", S, q[t]) / below[:, None]
+    return o, {"S": S, "n": n, "m": m}
+
+
+def matrix_memory(p: dict, w: Dict[str, torch.Tensor], pre: str, h: torch.Tensor, eps: float, state: Optional[dict]):
+    T, H, d, e = h.shape[0], p["heads"], p["dim"], p["vdim"]
+    q = (h @ w[pre + "q"].T).view(T, H, d) * d ** -0.5
+    k = (h @ w[pre + "k"].T).view(T, H, d)
+    v = (h @ w[pre + "v"].T).view(T, H, e)
+    gi, gf = log_gates(h @ w[pre + "i"].T, h @ w[pre + "f"].T, w[pre + "i.b"], w[pre + "f.b"], p["gate_cap"])
+    o, new_state = exp_gate_recurrence(q, k, v, gi, gf, state)
     y = rms_unit(o, eps).reshape(T, H * e) * w[pre + "norm"] * torch.sigmoid(h @ w[pre + "g"].T)
-    return y @ w[pre + "o"].T, {"S": S, "n": n, "m": m}
+    return y @ w[pre + "o"].T, new_state
 
 
 def parallel_mixer(p: dict, w, pre: str, h, start: int, eps: float, state: Optional[dict]):
@@ -191,6 +215,9 @@ def gated_ff(w, pre: str, h: torch.Tensor) -> torch.Tensor:
     return (silu(h @ w[pre + "gate"].T) * (h @ w[pre + "up"].T)) @ w[pre + "down"].T
 
 
+MARGINS: List[float] = []       # the smallest gap of logits that a choice of experts or of groups rested on, per call
+
+
 def choose_experts(z: torch.Tensor, top: int, groups: Optional[dict]):
     """z [T, E] router logits.  Scores are the softmax over all experts; experts outside the `keep` groups with the
     largest best score cannot be chosen; the `top` largest remaining scores are taken as they are."""
@@ -203,7 +230,13 @@ def choose_experts(z: torch.Tensor, top: int, groups: Optional[dict]):
         kept = torch.zeros(T, count, dtype=torch.bool)
         kept.scatter_(1, best.topk(keep, dim=-1).indices, True)
         allowed = kept[:, :, None].expand(T, count, E // count).reshape(T, E)
+        if keep < count:
+            ranked = z.view(T, count, E // count).max(dim=-1).values.sort(dim=-1, descending=True).values
+            MARGINS.append(float((ranked[:, keep - 1] - ranked[:, keep]).min()))
     chosen = torch.where(allowed, s, torch.full_like(s, -1.0)).topk(top, dim=-1).indices
+    ranked = torch.where(allowed, z, torch.full_like(z, -1e30)).sort(dim=-1, descending=True).values
+    if top < int(allowed[0].sum()):
+        MARGINS.append(float((ranked[:, top - 1] - ranked[:, top]).min()))
     return chosen, s.gather(1, chosen)
 
 
@@ -264,3 +297,100 @@ def greedy(cfg: dict, w, prompt: List[int], n: int) -> List[int]:
         logits, state = forward(cfg, w, out[-1:], state, pos)
         pos += 1
     return out
+
+
+def forward_in_pieces(cfg: dict, w, tokens: List[int], pieces: List[int]) -> torch.Tensor:
+    """The same logits, the tokens fed in portions of the given sizes from the state the portions before left."""
+    out, state, at = [], None, 0
+    for n in pieces:
+        logits, state = forward(cfg, w, tokens[at:at + n], state, at)
+        out.append(logits)
+        at += n
+    assert at == len(tokens)
+    return torch.cat(out)
+
+
+# ---------------------------------------------------------------------------------------------
+# random weights and model folders
+# ---------------------------------------------------------------------------------------------
+def random_weights(cfg: dict, seed: int, rank: int = 6) -> Dict[str, torch.Tensor]:
+    """Random tensors for a configuration, rounded to bfloat16 values (as a stored model's are).  `rank`: rows of a
+    gated-linear-attention layer's first decay matrix (the configuration does not give it)."""
+    g = torch.Generator().manual_seed(seed)
+    W = int(cfg["width"])
+
+    def rnd(*shape, s=1.0, mean=0.0):
+        return (torch.randn(*shape, generator=g) * s + mean).to(torch.bfloat16).to(DT)
+
+    def attention(m: str, a: dict, normed: bool):
+        H, G, d, e = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+        w[m + "q"], w[m + "k"], w[m + "v"] = rnd(H * d, W, s=W ** -0.5), rnd(G * d, W, s=W ** -0.5), rnd(G * e, W, s=W ** -0.5)
+        w[m + "o"] = rnd(W, H * e, s=(H * e) ** -0.5)
+        if normed:
+            w[m + "q.norm"], w[m + "k.norm"] = rnd(d, s=0.2, mean=1.0), rnd(d, s=0.2, mean=1.0)
+
+    def linear_qkvgo(m: str, r: dict):
+        H, d, e = r["heads"], r["dim"], r["vdim"]
+        w[m + "q"], w[m + "k"], w[m + "v"] = rnd(H * d, W, s=W ** -0.5), rnd(H * d, W, s=W ** -0.5), rnd(H * e, W, s=W ** -0.5)
+        w[m + "g"], w[m + "o"] = rnd(H * e, W, s=W ** -0.5), rnd(W, H * e, s=(H * e) ** -0.5)
+
+    def gated(m: str, F: int):
+        w[m + "gate"], w[m + "up"], w[m + "down"] = rnd(F, W, s=W ** -0.5), rnd(F, W, s=W ** -0.5), rnd(W, F, s=F ** -0.5)
+
+    w = {"embed": rnd(cfg["vocab"], W), "final.norm": rnd(W, s=0.1, mean=1.0), "head": rnd(cfg["vocab"], W, s=W ** -0.5)}
+    for i, layer in enumerate(cfg["layers"]):
+        if layer.get("weights_of") is not None:
+            continue
+        p, mx = f"l{i}.", layer["mixer"]
+        w[p + "norm1"] = rnd(W, s=0.1, mean=1.0)
+        if layer["type"] == "attention":
+            attention(p + "mix.", mx, True)
+        elif layer["type"] == "gla":
+            m = p + "mix."
+            linear_qkvgo(m, mx)
+            H, d = mx["heads"], mx["dim"]
+            rk = mx.get("rank", rank)
+            w[m + "a1"], w[m + "a2"] = rnd(rk, W, s=W ** -0.5), rnd(H * d, rk, s=2.0 * rk ** -0.5)
+            w[m + "a2.b"], w[m + "norm"] = rnd(H * d, s=1.0, mean=2.0), rnd(mx["vdim"], s=0.1, mean=1.0)
+        else:
+            attention(p + "mix.left.", mx["left"], False)
+            m, r = p + "mix.right.", mx["right"]
+            linear_qkvgo(m, r)
+            H = r["heads"]
+            w[m + "i"], w[m + "f"] = rnd(H, W, s=2.0 * W ** -0.5), rnd(H, W, s=2.0 * W ** -0.5)
+            w[m + "i.b"], w[m + "f.b"] = rnd(H, s=1.0), rnd(H, s=1.0, mean=2.0)
+            w[m + "norm"] = rnd(H * r["vdim"], s=0.1, mean=1.0)
+        mlp = layer.get("mlp")
+        if mlp is None:
+            continue
+        w[p + "norm2"] = rnd(W, s=0.1, mean=1.0)
+        if mlp["kind"] == "dense":
+            gated(p + "mlp.", mlp["ff"])
+            continue
+        w[p + "mlp.router"] = rnd(mlp["router"]["experts"], W, s=2.0 * W ** -0.5)
+        for x in range(mlp["router"]["experts"]):
+            gated(p + f"mlp.e{x}.", mlp["expert"]["ff"])
+        if mlp.get("shared") is not None:
+            gated(p + "mlp.shared.", mlp["shared"]["ff"])
+            w[p + "mlp.shared.sg"] = rnd(1, W, s=2.0 * W ** -0.5)
+    return w
+
+
+def save_folder(cfg: dict, w: Dict[str, torch.Tensor], out_dir: str, dtype=torch.bfloat16) -> str:
+    """Write config.json and model.safetensors (an independent writer of the file format)."""
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(out_dir, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    header, blobs, at = {}, [], 0
+    names = {torch.bfloat16: "BF16", torch.float32: "F32"}
+    for name, t in w.items():
+        t = t.to(dtype).contiguous()
+        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        header[name] = {"dtype": names[dtype], "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    head = json.dumps(header).encode()
+    head += b" " * (-len(head) % 8)
+    with open(os.path.join(out_dir, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(head)) + head + b"".join(blobs))
+    return out_dir
