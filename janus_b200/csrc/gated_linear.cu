@@ -41,33 +41,55 @@ constexpr float DEN_FLOOR = 1e-6f;
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
 // ---------------------------------------------------------------------------------------------------------------
-// alpha[t][c] = exp(logsigmoid(bias[c] + sum_j a2t[j][c] low[t][j]) inv_tau); TB tokens a block, a thread a channel
+// alpha[t][c] = exp(logsigmoid(bias[c] + sum_j a2t[j][c] low[t][j]) inv_tau); TB tokens a block, CPT channels a thread
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int TB = 8;
-__global__ void gla_decay_kernel(const float* __restrict__ proj, int ld, int low_col, int rank,
-                                 const float* __restrict__ a2t, const float* __restrict__ bias, float inv_tau,
-                                 float* __restrict__ alpha, int C, int T) {
-  extern __shared__ float low_s[];               // [TB][rank]
+constexpr int TB = 16;          // tokens a block
+constexpr int CPT = 2;          // channels a thread
+// The low-rank rows of the block's tokens lie in shared memory, padded with zeros to whole float4s: a thread reads four
+// numbers of a token's row with one load (all lanes the same address), and every weight it fetched serves TB tokens.
+__global__ void __launch_bounds__(128) gla_decay_kernel(const float* __restrict__ proj, int ld, int low_col, int rank,
+                                                        const float* __restrict__ a2t, const float* __restrict__ bias,
+                                                        float inv_tau, float* __restrict__ alpha, int C, int T) {
+  extern __shared__ __align__(16) float low_s[];               // [TB][rank4]
   jb::pdl_launch_dependents();
   jb::pdl_wait();
+  const int rank4 = (rank + 3) & ~3;
   const int t0 = blockIdx.x * TB, n = min(TB, T - t0);
-  for (int i = threadIdx.x; i < n * rank; i += blockDim.x)
-    low_s[i] = proj[(size_t)(t0 + i / rank) * ld + low_col + i % rank];
+  for (int i = threadIdx.x; i < TB * rank4; i += blockDim.x) {
+    const int u = i / rank4, j = i % rank4;
+    low_s[i] = (u < n && j < rank) ? proj[(size_t)(t0 + u) * ld + low_col + j] : 0.0f;
+  }
   __syncthreads();
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
-    float z[TB];
-    const float b = bias[c];
+  for (int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * CPT; c0 < C; c0 += gridDim.y * blockDim.x * CPT) {
+    float z[CPT][TB];
 #pragma unroll
-    for (int u = 0; u < TB; ++u) z[u] = b;
-    for (int j = 0; j < rank; ++j) {
-      const float w = a2t[(size_t)j * C + c];
+    for (int q = 0; q < CPT; ++q) {
+      const float b = c0 + q < C ? bias[c0 + q] : 0.0f;
 #pragma unroll
-      for (int u = 0; u < TB; ++u)
-        if (u < n) z[u] = fmaf(w, low_s[u * rank + j], z[u]);
+      for (int u = 0; u < TB; ++u) z[q][u] = b;
+    }
+    for (int j = 0; j < rank4; j += 4) {
+      float w[CPT][4];
+#pragma unroll
+      for (int q = 0; q < CPT; ++q)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[q][i] = (j + i < rank && c0 + q < C) ? a2t[(size_t)(j + i) * C + c0 + q] : 0.0f;
+#pragma unroll
+      for (int u = 0; u < TB; ++u) {
+        const float4 l = *reinterpret_cast<const float4*>(low_s + u * rank4 + j);
+#pragma unroll
+        for (int q = 0; q < CPT; ++q)
+          z[q][u] = fmaf(w[q][3], l.w, fmaf(w[q][2], l.z, fmaf(w[q][1], l.y, fmaf(w[q][0], l.x, z[q][u]))));
+      }
     }
 #pragma unroll
-    for (int u = 0; u < TB; ++u)
-      if (u < n) alpha[(size_t)(t0 + u) * C + c] = expf(log_sigmoid(z[u]) * inv_tau);
+    for (int u = 0; u < TB; ++u) {
+      if (u < n) {
+#pragma unroll
+        for (int q = 0; q < CPT; ++q)
+          if (c0 + q < C) alpha[(size_t)(t0 + u) * C + c0 + q] = expf(log_sigmoid(z[q][u]) * inv_tau);
+      }
+    }
   }
 }
 
@@ -355,9 +377,11 @@ __global__ void gated_linear_prefix_kernel(float* __restrict__ scratch, const fl
 JB_EXPORT int jb_gla_decay(const float* proj, int ld, int low_col, int rank, const float* a2t, const float* bias,
                            float inv_tau, float* alpha, int C, int T, cudaStream_t stream) {
   if (T <= 0) return 0;
-  JB_REFUSE(rank < 1 || (size_t)TB * rank * sizeof(float) > 48 * 1024, "gla_decay: a rank of %d", rank);
-  const int by = (C + 127) / 128 < 64 ? (C + 127) / 128 : 64;
-  jb::Launch cfg(dim3((T + TB - 1) / TB, by), dim3(128), (size_t)TB * rank * sizeof(float), stream);
+  const size_t smem = (size_t)TB * ((rank + 3) & ~3) * sizeof(float);
+  JB_REFUSE(rank < 1 || smem > 48 * 1024, "gla_decay: a rank of %d", rank);
+  const int per_block = 128 * CPT;
+  const int by = (C + per_block - 1) / per_block < 64 ? (C + per_block - 1) / per_block : 64;
+  jb::Launch cfg(dim3((T + TB - 1) / TB, by), dim3(128), smem, stream);
   return (int)cudaLaunchKernelEx(&cfg.c, gla_decay_kernel, proj, ld, low_col, rank, a2t, bias, inv_tau, alpha, C, T);
 }
 

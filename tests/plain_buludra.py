@@ -256,15 +256,18 @@ def expert_ff(m: dict, w, pre: str, h: torch.Tensor) -> torch.Tensor:
 # the whole model
 # ---------------------------------------------------------------------------------------------
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], state: Optional[dict] = None, start: int = 0,
-            layers_out: Optional[list] = None):
+            layers_out: Optional[list] = None, rounded: bool = False):
     """Logits [T, vocab] of `tokens` at positions start .., from `state` (None: a sequence's beginning), and the
-    state after them.  `layers_out` collects the residual stream after every layer."""
+    state after them.  `layers_out` collects the residual stream after every layer.  `rounded`: what every norm hands
+    to the products behind it is rounded to bfloat16 values, the one rounding of a bfloat16 engine that reaches the
+    recurrent mixers (their projections, gates and states are 32-bit from there on)."""
     eps = cfg["norm"]["eps"]
+    handed = (lambda h: h.to(torch.bfloat16).to(DT)) if rounded else (lambda h: h)
     x = w["embed"][torch.tensor(tokens)]
     new_state = {}
     for i, layer in enumerate(cfg["layers"]):
         pre = f"l{layer.get('weights_of', i)}."
-        h = rms_unit(x, eps) * w[pre + "norm1"]
+        h = handed(rms_unit(x, eps) * w[pre + "norm1"])
         st = None if state is None else state[i]
         kind, p = layer["type"], layer["mixer"]
         if kind == "attention":
@@ -278,11 +281,11 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], state: Opt
         x = x + y
         m = layer.get("mlp")
         if m is not None:
-            h = rms_unit(x, eps) * w[pre + "norm2"]
+            h = handed(rms_unit(x, eps) * w[pre + "norm2"])
             x = x + (gated_ff(w, pre + "mlp.", h) if m["kind"] == "dense" else expert_ff(m, w, pre + "mlp.", h))
         if layers_out is not None:
             layers_out.append(x.clone())
-    logits = (rms_unit(x, eps) * w["final.norm"]) @ w["head"].T
+    logits = handed(rms_unit(x, eps) * w["final.norm"]) @ w["head"].T
     cap = cfg.get("logit_softcap")
     if cap:
         logits = cap * torch.tanh(logits / cap)
