@@ -1708,7 +1708,7 @@ def gated_linear_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, q_
     (float32 [T, heads], written), `decays` is what `exp_gates` left ([T, heads, 4]: a_t and b_t one number a head),
     a normalizer n <- a_t n + b_t k_t walks along, divisors[t, h] = max(|n . q|, exp(-m_t)) + 1e-6, and a slot's state
     row holds per head [dim, vdim] then [dim] of n.  With a workspace, steps whose longest sequence brings more than
-    two segments of tokens run in passes over segments (4 launches); else one launch."""
+    256 tokens run in passes over segments of 64 to 256 tokens (4 launches); else one launch."""
     T = proj.shape[0]
     scalar = divisors is not None
     _need(proj, "projections", torch.float32)
@@ -1726,7 +1726,9 @@ def gated_linear_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, q_
         raise KernelError("gated_linear_scan: the projections' columns reach past the rows")
     seg, scratch, seg_decay = 0, None, None
     if workspace is not None and max_q_len > 2 * GATED_LINEAR_SEGMENT:
-        seg = GATED_LINEAR_SEGMENT
+        # the blocks are laid out as the state-space recurrence's (a segment, a head, 64 value columns; four blocks an SM
+        # up to 128 rows of state, else two): the segment length that fills the SMs in whole waves is picked the same way
+        seg = mamba2_segment_for(n_seqs, max_q_len, heads, dim, vdim)
         tiles = (max_q_len + seg - 1) // seg
         scratch = workspace.get("gated_linear_segments", (n_seqs * tiles * heads * per_head,), torch.float32)
         seg_decay = workspace.get("gated_linear_segment_decays", (n_seqs * tiles * heads * (1 if scalar else dim),),
