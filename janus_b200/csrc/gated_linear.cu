@@ -16,7 +16,8 @@
 //              run into (sum of f, what the maximum would be from minus infinity), chains the runs, and walks again.
 // gated_linear_scan: a block owns one (sequence or segment, head, block of EB value columns); a thread owns two value
 //              columns and a quarter of the rows of S in registers and walks the tokens in order (chunks of CT tokens
-//              are staged in shared memory); the four partial sums of o meet by shuffles in a fixed order.  The
+//              come into shared memory by asynchronous copies, the next chunk while the current one is walked); the
+//              four partial sums of o meet by shuffles in a fixed order.  The
 //              normalizer is a column of its own that the block's first warp carries.  The state is read from and
 //              written back to the sequence's slot, so prompts, portions of prompts and single tokens are the same code.
 //
@@ -34,7 +35,7 @@ namespace {
 
 constexpr int PARTS = 4;      // threads that share a value column (each a quarter of the rows)
 constexpr int EB = 64;        // value columns a block owns, two a thread
-constexpr int CT = 16;        // tokens staged at a time
+constexpr int CT = 8;         // tokens staged at a time, in each of two buffers
 constexpr int THREADS = EB / 2 * PARTS;
 constexpr float DEN_FLOOR = 1e-6f;
 
@@ -148,28 +149,43 @@ __global__ void __launch_bounds__(GT) exp_gates_kernel(const float* __restrict__
 
 enum { WHOLE = 0, LOCAL = 1, FROM_START = 3 };
 
+// Asynchronous copies global -> shared; with `in` false nothing is read and the destination is filled with zeros.
+__device__ __forceinline__ void copy_async_16(float* dst, const float* src, bool in) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int n = in ? 16 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void copy_async_4(float* dst, const float* src, bool in) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int n = in ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copy_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+constexpr int VEC_QK = 1, VEC_V = 2;   // which rows of a token are whole, aligned 16-byte vectors in global memory
+
 // RMAX: rows of S a thread holds (a multiple of 4, 4 RMAX >= d); shared rows are padded to 4 RMAX with zeros.
 // SCALAR: one decay and one input scale per head and token (`dec` is the float4 gates [T][H]); else `dec` holds a decay
 // per key channel, [T][dec_ld] with head h at column h d.  NORM: the normalizer column and the divisor (SCALAR only).
 // State of a head, in the slot and in the segments' scratch alike: [d][e] floats of S, then with NORM [d] of n.
+// The tokens' rows come into shared memory by asynchronous copies, CT tokens at a time into one of two buffers: the
+// next chunk is on its way while the current one is walked.  The copies are plain, so the query's scale multiplies
+// the sums and the input's scale the values where they are used.
 template <int RMAX, int PHASE, bool SCALAR, bool NORM>
 __global__ void __launch_bounds__(THREADS, RMAX <= 32 ? 4 : 2) gated_linear_scan_kernel(
     const float* __restrict__ proj, int ld, int q_col, int k_col, int v_col, float q_scale,
     const float* __restrict__ dec, int dec_ld, float* __restrict__ out, float* __restrict__ den,
     float* __restrict__ state, long long state_ld, const int* __restrict__ q_start, const int* __restrict__ seq_slot,
-    int H, int d, int e, int seg_len, int tiles_per_seq, float* __restrict__ scratch) {
+    int H, int d, int e, int seg_len, int tiles_per_seq, float* __restrict__ scratch, int vec) {
   constexpr int phase = PHASE;
   constexpr int DP = PARTS * RMAX;         // padded rows
   // a part's rows start four floats after the part before ends: the four parts of a column read their 16 bytes
   // from different banks
   constexpr int PS = RMAX + 4;             // floats from part to part
   constexpr int TS = PARTS * PS;           // floats from token to token
-  extern __shared__ __align__(16) float smem[];          // q [CT][TS], k [CT][TS], v [CT][EB], gates [CT][4], a [CT][TS]
-  float* q_s = smem;
-  float* k_s = q_s + CT * TS;
-  float* v_s = k_s + CT * TS;
-  float* g_s = v_s + CT * EB;
-  float* a_s = g_s + CT * 4;
+  constexpr int BUF = (SCALAR ? 2 : 3) * CT * TS + CT * EB + CT * 4;   // floats of one buffer
+  extern __shared__ __align__(16) float smem[];          // twice: q [CT][TS], k [CT][TS], v [CT][EB], gates [CT][4], a [CT][TS]
   jb::pdl_launch_dependents();
   const int seq = blockIdx.x / tiles_per_seq, seg = blockIdx.x % tiles_per_seq;
   const int h = blockIdx.y, e0 = blockIdx.z * EB;
@@ -186,6 +202,55 @@ __global__ void __launch_bounds__(THREADS, RMAX <= 32 ? 4 : 2) gated_linear_scan
   float* st = state + (size_t)seq_slot[seq] * state_ld + (size_t)h * d * ex;
   float* sc = scratch ? scratch + (((size_t)blockIdx.x * H + h) * d) * ex : nullptr;
   const float* init = phase == WHOLE ? st : phase == FROM_START ? sc : nullptr;
+
+  // the rows of the tokens [c0, c0 + n) on their way into buffer `b`
+  auto stage = [&](int b, int c0) {
+    const int n = min(CT, t1 - c0);
+    float* q_b = smem + b * BUF;
+    float* k_b = q_b + CT * TS;
+    float* v_b = k_b + CT * TS;
+    float* g_b = v_b + CT * EB;
+    float* a_b = g_b + CT * 4;
+    if (SCALAR && threadIdx.x < n * 4)
+      copy_async_4(g_b + threadIdx.x, dec + ((size_t)(c0 + (threadIdx.x >> 2)) * H + h) * 4 + (threadIdx.x & 3), true);
+    if (vec & VEC_QK) {
+      for (int idx = threadIdx.x; idx < n * (DP / 4); idx += THREADS) {
+        const int tt = idx / (DP / 4), r = (idx % (DP / 4)) * 4;
+        const bool in = r < d;                     // d is a multiple of 4 here: a group is inside or outside as a whole
+        const size_t row = (size_t)(c0 + tt), at_col = (size_t)h * d + (in ? r : 0);
+        const int at = tt * TS + (r / RMAX) * PS + r % RMAX;
+        if (phase != LOCAL) copy_async_16(q_b + at, proj + row * ld + q_col + at_col, in);
+        copy_async_16(k_b + at, proj + row * ld + k_col + at_col, in);
+        if (!SCALAR) copy_async_16(a_b + at, dec + row * dec_ld + at_col, in);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < n * DP; idx += THREADS) {
+        const int tt = idx / DP, r = idx % DP;
+        const bool in = r < d;
+        const size_t row = (size_t)(c0 + tt), at_col = (size_t)h * d + (in ? r : 0);
+        const int at = tt * TS + (r / RMAX) * PS + r % RMAX;
+        if (phase != LOCAL) copy_async_4(q_b + at, proj + row * ld + q_col + at_col, in);
+        copy_async_4(k_b + at, proj + row * ld + k_col + at_col, in);
+        if (!SCALAR) copy_async_4(a_b + at, dec + row * dec_ld + at_col, in);
+      }
+    }
+    if (vec & VEC_V) {
+      for (int idx = threadIdx.x; idx < n * (EB / 4); idx += THREADS) {
+        const int tt = idx / (EB / 4), c = (idx % (EB / 4)) * 4;
+        const bool in = e0 + c < e;                // e is a multiple of 4 here
+        copy_async_16(v_b + tt * EB + c, proj + (size_t)(c0 + tt) * ld + v_col + (size_t)h * e + (in ? e0 + c : 0), in);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < n * EB; idx += THREADS) {
+        const int tt = idx / EB, c = idx % EB;
+        const bool in = e0 + c < e;
+        copy_async_4(v_b + tt * EB + c, proj + (size_t)(c0 + tt) * ld + v_col + (size_t)h * e + (in ? e0 + c : 0), in);
+      }
+    }
+  };
+
+  stage(0, t0);
+  copy_async_commit();
   float S0[RMAX], S1[RMAX], Sn[NORM ? RMAX : 1];
 #pragma unroll
   for (int i = 0; i < RMAX; ++i) {
@@ -194,61 +259,29 @@ __global__ void __launch_bounds__(THREADS, RMAX <= 32 ? 4 : 2) gated_linear_scan
     S1[i] = (init && r < d && j1 < e) ? init[(size_t)r * e + j1] : 0.0f;
     if constexpr (NORM) Sn[i] = (init && carries_n && r < d) ? init[(size_t)d * e + r] : 0.0f;
   }
-  for (int c0 = t0; c0 < t1; c0 += CT) {
+  int b = 0;
+  for (int c0 = t0; c0 < t1; c0 += CT, b ^= 1) {
     const int n = min(CT, t1 - c0);
+    if (c0 + CT < t1) stage(b ^ 1, c0 + CT);
+    copy_async_commit();                           // an empty group behind the last chunk
+    copy_async_wait_all_but_one();                 // this chunk's copies have landed
     __syncthreads();
-    if (SCALAR) {
-      if (threadIdx.x < CT * 4) {
-        const int tt = threadIdx.x >> 2;
-        g_s[threadIdx.x] = tt < n ? dec[((size_t)(c0 + tt) * H + h) * 4 + (threadIdx.x & 3)] : 0.0f;
-      }
-    }
-    // eight loads of each kind are in flight before they are stored
-    for (int base = 0; base < n * DP; base += 8 * THREADS) {
-      float qv[8], kv[8], av[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int idx = base + u * THREADS + threadIdx.x;
-        const int tt = idx / DP, r = idx % DP;
-        const bool in = idx < n * DP && r < d;
-        const float* row = proj + (size_t)(c0 + (in ? tt : 0)) * ld + h * d + (in ? r : 0);
-        qv[u] = (in && phase != LOCAL) ? row[q_col] * q_scale : 0.0f;
-        kv[u] = in ? row[k_col] : 0.0f;
-        if (!SCALAR) av[u] = in ? dec[(size_t)(c0 + tt) * dec_ld + h * d + r] : 0.0f;
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int idx = base + u * THREADS + threadIdx.x;
-        if (idx < n * DP) {
-          const int r = idx % DP;
-          const int at = (idx / DP) * TS + (r / RMAX) * PS + r % RMAX;
-          if (phase != LOCAL) q_s[at] = qv[u];
-          k_s[at] = kv[u];
-          if (!SCALAR) a_s[at] = av[u];
-        }
-      }
-    }
-    {
-      float vv[CT * EB / THREADS];
-#pragma unroll
-      for (int u = 0; u < CT * EB / THREADS; ++u) {
-        const int idx = u * THREADS + threadIdx.x;
-        const int tt = idx / EB, c = idx % EB;
-        const bool in = tt < n && e0 + c < e;
-        vv[u] = in ? proj[(size_t)(c0 + tt) * ld + v_col + h * e + e0 + c] : 0.0f;
-        // the input's scale goes onto the values: take (k v^T) = k (take v)^T
-        if (SCALAR && in) vv[u] *= dec[((size_t)(c0 + tt) * H + h) * 4 + 1];
-      }
-#pragma unroll
-      for (int u = 0; u < CT * EB / THREADS; ++u) v_s[u * THREADS + threadIdx.x] = vv[u];
-    }
-    __syncthreads();
+    const float* q_s = smem + b * BUF;
+    const float* k_s = q_s + CT * TS;
+    const float* v_s = k_s + CT * TS;
+    const float* g_s = v_s + CT * EB;
+    const float* a_s = g_s + CT * 4;
     for (int tt = 0; tt < n; ++tt) {
-      const float2 v = *reinterpret_cast<const float2*>(v_s + tt * EB + 2 * col);
+      float2 v = *reinterpret_cast<const float2*>(v_s + tt * EB + 2 * col);
       const float4* qr = reinterpret_cast<const float4*>(q_s + tt * TS + part * PS);
       const float4* kr = reinterpret_cast<const float4*>(k_s + tt * TS + part * PS);
       const float4* ar = reinterpret_cast<const float4*>(a_s + tt * TS + part * PS);
       const float keep = SCALAR ? g_s[tt * 4] : 0.0f, take = SCALAR ? g_s[tt * 4 + 1] : 0.0f;
+      if (SCALAR) {
+        // the input's scale goes onto the values: take (k v^T) = k (take v)^T
+        v.x *= take;
+        v.y *= take;
+      }
       float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f, b3 = 0.0f;
       float n0 = 0.0f, n1 = 0.0f;
 #pragma unroll
@@ -298,18 +331,19 @@ __global__ void __launch_bounds__(THREADS, RMAX <= 32 ? 4 : 2) gated_linear_scan
         acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
         if (part == 0) {
           float* orow = out + (size_t)(c0 + tt) * H * e + (size_t)h * e;
-          if (j0 < e) orow[j0] = acc0;
-          if (j1 < e) orow[j1] = acc1;
+          if (j0 < e) orow[j0] = acc0 * q_scale;
+          if (j1 < e) orow[j1] = acc1 * q_scale;
         }
         if constexpr (NORM) if (carries_n) {
           float nq = n0 + n1;
           nq += __shfl_xor_sync(0xffffffffu, nq, 1);
           nq += __shfl_xor_sync(0xffffffffu, nq, 2);
           if (threadIdx.x == 0 && blockIdx.z == 0)
-            den[(size_t)(c0 + tt) * H + h] = fmaxf(fabsf(nq), g_s[tt * 4 + 2]) + DEN_FLOOR;
+            den[(size_t)(c0 + tt) * H + h] = fmaxf(fabsf(nq * q_scale), g_s[tt * 4 + 2]) + DEN_FLOOR;
         }
       }
     }
+    __syncthreads();                               // the buffer is free for the chunk after the next
   }
   float* dst = phase == LOCAL ? sc : (last ? st : nullptr);
   if (dst == nullptr) return;
@@ -402,7 +436,7 @@ template <int RMAX, int PHASE, bool SCALAR, bool NORM>
 cudaError_t launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const float* proj, int ld, int q_col, int k_col,
                         int v_col, float q_scale, const float* dec, int dec_ld, float* out, float* den, float* state,
                         long long state_ld, const int* q_start, const int* seq_slot, int H, int d, int e, int seg,
-                        int tiles, float* scratch) {
+                        int tiles, float* scratch, int vec) {
   auto k = gated_linear_scan_kernel<RMAX, PHASE, SCALAR, NORM>;
   if (smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -410,7 +444,7 @@ cudaError_t launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const float
   }
   jb::Launch cfg(grid, dim3(THREADS), smem, stream);
   return cudaLaunchKernelEx(&cfg.c, k, proj, ld, q_col, k_col, v_col, q_scale, dec, dec_ld, out, den, state, state_ld,
-                            q_start, seq_slot, H, d, e, seg, tiles, scratch);
+                            q_start, seq_slot, H, d, e, seg, tiles, scratch, vec);
 }
 
 template <int PHASE, bool SCALAR, bool NORM, typename... A>
@@ -428,7 +462,12 @@ int scan_all(const float* proj, int ld, int q_col, int k_col, int v_col, float q
              cudaStream_t stream) {
   const int rmax = d <= 32 ? 8 : d <= 64 ? 16 : d <= 128 ? 32 : 64;
   const int ts = PARTS * (rmax + 4);
-  const size_t smem = (size_t)((SCALAR ? 2 : 3) * CT * ts + CT * EB + CT * 4) * sizeof(float);
+  const size_t smem = 2 * (size_t)((SCALAR ? 2 : 3) * CT * ts + CT * EB + CT * 4) * sizeof(float);   // two buffers
+  // rows that are whole 16-byte vectors at aligned addresses are copied 16 bytes at a time
+  const bool base16 = ((uintptr_t)proj & 15) == 0 && ld % 4 == 0;
+  const bool dec16 = SCALAR || (((uintptr_t)dec & 15) == 0 && dec_ld % 4 == 0);
+  const int vec = (base16 && dec16 && d % 4 == 0 && q_col % 4 == 0 && k_col % 4 == 0 ? VEC_QK : 0) |
+                  (base16 && e % 4 == 0 && v_col % 4 == 0 ? VEC_V : 0);
   const bool segmented = seg_len > 0;
   const int tiles = segmented ? (max_q_len + seg_len - 1) / seg_len : 1;
   const int seg = segmented ? seg_len : 0x40000000;
@@ -438,11 +477,12 @@ int scan_all(const float* proj, int ld, int q_col, int k_col, int v_col, float q
   if (!segmented) {
     err = launch_scan_r<WHOLE, SCALAR, NORM>(rmax, grid, smem, stream, proj, ld, q_col, k_col, v_col, q_scale, dec,
                                              dec_ld, out, den, state, state_ld, q_start, seq_slot, H, d, e, seg, tiles,
-                                             scratch);
+                                             scratch, vec);
     return (int)err;
   }
   err = launch_scan_r<LOCAL, SCALAR, NORM>(rmax, grid, smem, stream, proj, ld, q_col, k_col, v_col, q_scale, dec, dec_ld,
-                                           out, den, state, state_ld, q_start, seq_slot, H, d, e, seg, tiles, scratch);
+                                           out, den, state, state_ld, q_start, seq_slot, H, d, e, seg, tiles, scratch,
+                                           vec);
   if (err != cudaSuccess) return (int)err;
   {
     jb::Launch cfg(dim3(n_seqs * tiles, H), dim3(SCALAR ? 32 : (d <= 64 ? 64 : d <= 128 ? 128 : 256)), 0, stream);
@@ -458,7 +498,7 @@ int scan_all(const float* proj, int ld, int q_col, int k_col, int v_col, float q
   }
   err = launch_scan_r<FROM_START, SCALAR, NORM>(rmax, grid, smem, stream, proj, ld, q_col, k_col, v_col, q_scale, dec,
                                                 dec_ld, out, den, state, state_ld, q_start, seq_slot, H, d, e, seg,
-                                                tiles, scratch);
+                                                tiles, scratch, vec);
   return (int)err;
 }
 }  // namespace

@@ -555,19 +555,21 @@ def _step_tensors(lengths, slots):
 @pytest.mark.parametrize("H,d,e", [(4, 8, 16), (3, 5, 9), (2, 64, 64), (1, 200, 24), (2, 32, 40), (2, 96, 130), (1, 256, 16),
                                    (2, 33, 65)])
 @pytest.mark.parametrize("kind", ["decays", "gates"])
-def test_the_recurrence_kernels_against_the_plain_recurrences(kind, H, d, e):
+@pytest.mark.parametrize("lead", [1, 0])
+def test_the_recurrence_kernels_against_the_plain_recurrences(lead, kind, H, d, e):
     """Three sequences of unequal lengths in slots out of order: a prompt step (one sequence long enough to run in
     segments), a second portion from the state the first left, then single tokens; outputs, the divisors' effect and
     the final state against the plain recurrence run in one piece.  With decays per key channel, and with exponential
     gates, a normalizer and a running maximum."""
     from janus_b200.engine.workspace import Workspace
     from janus_b200.kernels import ops
-    g = torch.Generator().manual_seed(d * 100 + e)
+    g = torch.Generator().manual_seed(d * 100 + e + lead)
     gates = kind == "gates"
     total, slots = (700, 3, 71), [2, 0, 3]
     rank, tau, cap = 3, 8.0, 6.0
-    ld = 2 * H * d + H * e + (2 * H if gates else rank) + 1
-    q_col, k_col, v_col, x_col = 1, 1 + H * d, 1 + 2 * H * d, 1 + 2 * H * d + H * e
+    ld = 2 * H * d + H * e + (2 * H if gates else rank) + lead
+    ld += 0 if lead else -ld % 4
+    q_col, k_col, v_col, x_col = lead, lead + H * d, lead + 2 * H * d, lead + 2 * H * d + H * e
     seqs = [torch.randn(n, ld, generator=g) for n in total]
     for s in seqs:
         s[:, x_col:] *= 3.0
