@@ -239,9 +239,10 @@ class BuludraConfig:
         return ()
 
     def owner(self, i: int) -> int:
-        """The layer whose tensors layer i uses."""
-        w = self.layers[i].weights_of
-        return i if w is None else w
+        """The layer whose tensors layer i uses (a layer may name one that names another in turn)."""
+        while self.layers[i].weights_of is not None:
+            i = self.layers[i].weights_of
+        return i
 
     def with_tensor_shapes(self, shape_of) -> "BuludraConfig":
         """The configuration with the sizes that only a tensor's shape gives: the rank of a gated-linear-attention
@@ -255,7 +256,7 @@ class BuludraConfig:
                     layers[i] = replace(layer, mixer=replace(layer.mixer, rank=int(shape[0])))
         for i, layer in enumerate(layers):
             if layer.weights_of is not None:
-                layers[i] = replace(layer, mixer=layers[layer.weights_of].mixer)
+                layers[i] = replace(layer, mixer=layers[self.owner(i)].mixer)
         return replace(self, layers=tuple(layers))
 
     @classmethod
@@ -281,8 +282,14 @@ class BuludraConfig:
             j = layer.weights_of
             if j is None:
                 continue
-            if j >= len(layers) or j == i or layers[j].weights_of is not None:
-                raise ConfigError(f"key 'layers[{i}].weights_of' must name another layer that has tensors of its own, got {j}")
+            seen = {i}
+            while j is not None and j < len(layers) and j not in seen:      # a chain ends at a layer with tensors
+                seen.add(j)
+                j, last = layers[j].weights_of, j
+            if j is not None:
+                raise ConfigError(f"key 'layers[{i}].weights_of' must lead to another layer that has tensors of its own, "
+                                  f"got {layer.weights_of}")
+            j = last
             if (layers[j].type, layers[j].mixer, layers[j].mlp) != (layer.type, layer.mixer, layer.mlp):
                 raise ConfigError(f"key 'layers[{i}]': a layer that uses layer {j}'s tensors must have its sizes and constants")
         return cls(vocab=r.integer("vocab"), width=r.integer("width"), eps=norm.number("eps"), layers=tuple(layers),

@@ -280,6 +280,10 @@ def test_configuration_is_read_by_key_and_written_back():
     assert c.layers[4].mixer.left.rot_dims == 0 and c.layers[0].mixer.left.rot_dims == 8 and c.layers[3].weights_of == 1
     assert c.owner(3) == 1 and c.owner(4) == 4 and c.layers[4].mlp.shared_ff == 0 and c.logit_softcap == 8.0
     assert arch.config_class.from_dict(CFG_B).logit_softcap == 0.0
+    # a layer may name a layer that itself uses another's tensors: the chain ends at the one that has them
+    chain = copy.deepcopy(CFG_A)
+    chain["layers"].append(dict(copy.deepcopy(_A1), weights_of=3))
+    assert [arch.config_class.from_dict(chain).owner(i) for i in range(6)] == [0, 1, 2, 1, 4, 1]
     # the rank of a decay's projection is what the tensor's shape says, where there is a tensor
     c2 = c.with_tensor_shapes(lambda name: (9, 64) if name == "l2.mix.a1" else None)
     assert c2.layers[2].mixer.rank == 9 and c.layers[2].mixer.rank == 5
@@ -290,6 +294,7 @@ def test_configuration_is_read_by_key_and_written_back():
                               (("layers", 1, "mlp", "router", "groups", "count"), 4, "groups"),
                               (("layers", 1, "mlp", "router", "groups", "keep"), 4, "groups"),
                               (("layers", 3, "weights_of"), 3, "weights_of"), (("layers", 3, "weights_of"), 2, "layers"),
+                              (("layers", 3, "weights_of"), 9, "weights_of"),
                               (("layers", 0, "mixer", "right"), None, "right"), (("layers", 2, "mixer", "tau"), -1.0, "tau")):
         bad = copy.deepcopy(CFG_A)
         at = bad
